@@ -1,0 +1,117 @@
+/* C ABI of libsparseattn_b200.so -- the two-stage block-sparse attention forward
+ * path of tomatillos/sparseattention on NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and element strides; no
+ * torch types cross this boundary.  The caller owns every buffer (inputs,
+ * outputs, workspace).  All work is enqueued on the given CUDA stream of the
+ * current device and the calls do not synchronise.  Return value: 0 on success,
+ * a negative SA_ERR_* otherwise (nothing is launched on an argument error).
+ * The library never falls back to the CPU.
+ */
+#ifndef SA_B200_H_
+#define SA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SA_ABI_VERSION 1
+
+/* status codes */
+#define SA_OK                     0
+#define SA_ERR_INVALID_ARGUMENT  -1   /* null pointer, non-positive size, block size not dividing S */
+#define SA_ERR_UNSUPPORTED       -2   /* shape / dtype / layout outside the supported set */
+#define SA_ERR_WORKSPACE         -3   /* workspace missing or too small */
+#define SA_ERR_CUDA              -4   /* a CUDA runtime / driver call failed (launch error included) */
+#define SA_ERR_NO_DEVICE         -5   /* no usable sm_100 device is current */
+
+/* element types of Q, K, V, O */
+#define SA_DTYPE_F32   0
+#define SA_DTYPE_F16   1
+#define SA_DTYPE_BF16  2
+
+/* attention kernel selection */
+#define SA_IMPL_AUTO     0   /* tcgen05 kernel when the call is inside its supported set, else the SIMT kernel */
+#define SA_IMPL_SIMT     1   /* generic fp32-accumulate CUDA-core kernel (any dtype, any block size) */
+#define SA_IMPL_TCGEN05  2   /* TMA + tcgen05/TMEM kernel; SA_ERR_UNSUPPORTED outside its set */
+
+/* values written to *dev_status by the attention kernel (0 = no device-side problem) */
+#define SA_DEV_OK             0
+#define SA_DEV_WAIT_EXPIRED   1   /* a bounded mbarrier wait ran out; the output is not valid */
+#define SA_DEV_BAD_INDEX      2   /* a kv-block id outside [0, Sk/BLOCK_K) was found in a list */
+
+int sa_abi_version(void);
+const char* sa_status_str(int status);
+
+/* Number of distinct mask planes of a [B,H,Sq,Sk] mask whose batch / head strides
+ * may be 0 (an expanded, broadcast mask: sparse_attn_kernel.py:154).  The
+ * classifier reads and lists each distinct plane once: outputs have leading dims
+ * [*Bu, *Hu] with Bu = (stride_b == 0 ? 1 : B), Hu = (stride_h == 0 ? 1 : H). */
+int sa_unique_planes(int B, int H, int64_t stride_b, int64_t stride_h, int* Bu, int* Hu);
+
+/* Bytes of scratch sa_classify_mask needs (per-cell flag bytes between its two kernels). */
+size_t sa_classify_workspace_bytes(int Bu, int Hu, int Sq, int Sk);
+
+/* Stage 1: block classifier.  Replaces compute_mask_kernel / _compute_mask_inner
+ * (sparseattention/mask_utils.py:85-107, 47-82).
+ *
+ * mask: bool bytes [B,H,Sq,Sk] (non-zero = attend) with element strides; stride_k
+ *   must be 1 and every row start 16-byte aligned (else SA_ERR_UNSUPPORTED: make it
+ *   contiguous first).  Sq % BLOCK_Q == 0 and Sk % BLOCK_K == 0 as in
+ *   mask_utils.py:89-90; BLOCK_Q and BLOCK_K multiples of 32.
+ * full_ids, part_ids: int32 [Bu,Hu,Sq/BLOCK_Q,Sk/BLOCK_K] contiguous; ascending kv-block
+ *   ids of the fully-unmasked / partially-masked tiles of each query block, tail -1
+ *   (mask_utils.py:72-79; the reference leaves the tail uninitialised).
+ * full_lens, part_lens: int32 [Bu,Hu,Sq/BLOCK_Q] contiguous (mask_utils.py:81-82).
+ * packed_bits: optional uint32 [Bu,Hu,Sk/32,Sq]; bit j of word [.,.,c,r] = mask[.,.,r,32c+j].
+ *   Stage 2's tcgen05 kernel stages partial tiles from this plane instead of the byte mask.
+ * workspace: sa_classify_workspace_bytes() bytes of device memory. */
+int sa_classify_mask(const uint8_t* mask,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_q, int64_t stride_k,
+                     int B, int H, int Sq, int Sk, int BLOCK_Q, int BLOCK_K,
+                     int32_t* full_ids, int32_t* full_lens,
+                     int32_t* part_ids, int32_t* part_lens,
+                     uint32_t* packed_bits,
+                     void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/* Whether SA_IMPL_AUTO would pick the tcgen05 kernel for this call (1) or the SIMT kernel (0). */
+int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int Sk,
+                         const void* q, const void* k, const void* v,
+                         const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                         int has_packed_bits);
+
+/* Stage 2: block-sparse attention forward.  Replaces sparse_attention /
+ * sparse_attention_kernel / _sparse_inner (sparseattention/sparse_attn_kernel.py:149-185,
+ * 72-146, 10-63): per query block, a mask-free loop over the full list, then a masked
+ * loop over the partial list, online softmax in base 2 with fp32 state, O = acc / l.
+ * Rows with no attended key produce 0 (the reference produces NaN; torch SDPA gives 0).
+ *
+ * q,o: [B,H,Sq,D]; k,v: [B,H,Sk,D]; *_strides: 4 element strides each (b,h,s,d).
+ * mask: bool bytes [B,H,Sq,Sk] with 4 element strides (0 allowed); read by the SIMT kernel.
+ * packed_bits: uint32 plane from sa_classify_mask with (b,h) strides in words, or NULL
+ *   (required by the tcgen05 kernel).
+ * full_ids/part_ids: int32 with 4 element strides (b,h,q,k); full_lens/part_lens: int32 with
+ *   3 element strides (b,h,q).  Only ids[..., :len] is read; they are trusted like the
+ *   reference trusts a caller-supplied MaskMetadata (sparse_attn_kernel.py:157-163).
+ * scale_log2: softmax scale already multiplied by log2(e) (sparse_attn_kernel.py:152).
+ * dev_status: optional device int32, set non-zero by the kernel on a device-side problem. */
+int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
+                const int64_t* q_strides, const int64_t* k_strides,
+                const int64_t* v_strides, const int64_t* o_strides,
+                int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
+                const uint8_t* mask, const int64_t* mask_strides,
+                const uint32_t* packed_bits, int64_t bits_stride_b, int64_t bits_stride_h,
+                const int32_t* full_ids, const int64_t* full_ids_strides,
+                const int32_t* full_lens, const int64_t* full_lens_strides,
+                const int32_t* part_ids, const int64_t* part_ids_strides,
+                const int32_t* part_lens, const int64_t* part_lens_strides,
+                float scale_log2, int impl, int32_t* dev_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SA_B200_H_ */

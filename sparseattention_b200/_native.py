@@ -1,0 +1,247 @@
+"""ctypes binding of ``libsparseattn_b200.so`` (``include/sa_b200.h``) and the two
+``torch.library`` custom ops built on it.
+
+There is no CPU implementation and no fallback: the ops accept CUDA tensors only and
+raise if the library is missing or a call is outside the supported set.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import List, Tuple
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libsparseattn_b200.so")
+
+# mirrors of the header's constants
+SA_ABI_VERSION = 1
+SA_OK = 0
+SA_DTYPE_F32, SA_DTYPE_F16, SA_DTYPE_BF16 = 0, 1, 2
+SA_IMPL_AUTO, SA_IMPL_SIMT, SA_IMPL_TCGEN05 = 0, 1, 2
+SA_DEV_OK, SA_DEV_WAIT_EXPIRED, SA_DEV_BAD_INDEX = 0, 1, 2
+
+IMPLS = {"auto": SA_IMPL_AUTO, "simt": SA_IMPL_SIMT, "tcgen05": SA_IMPL_TCGEN05}
+_DTYPES = {torch.float32: SA_DTYPE_F32, torch.float16: SA_DTYPE_F16, torch.bfloat16: SA_DTYPE_BF16}
+
+# every symbol the header declares, with its ctypes signature
+_i, _i64, _p, _sz, _f = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_float
+_pi = ctypes.POINTER(ctypes.c_int)
+SYMBOLS = {
+    "sa_abi_version": (_i, []),
+    "sa_status_str": (ctypes.c_char_p, [_i]),
+    "sa_unique_planes": (_i, [_i, _i, _i64, _i64, _pi, _pi]),
+    "sa_classify_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "sa_classify_mask": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "sa_attn_uses_tcgen05": (_i, [_i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i]),
+    "sa_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p,
+                         _i, _i, _i, _i, _i, _i, _i, _i,
+                         _p, _p, _p, _i64, _i64,
+                         _p, _p, _p, _p, _p, _p, _p, _p,
+                         _f, _i, _p, _p]),
+}
+
+_lib = None
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def load_library():
+    """Loads the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise NativeLibraryError(
+            f"{LIB_PATH} is missing: build it with `python -m sparseattention_b200.build` "
+            "(there is no CPU or PyTorch fallback for these ops)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    if lib.sa_abi_version() != SA_ABI_VERSION:
+        raise NativeLibraryError("libsparseattn_b200.so has a different ABI version; rebuild it")
+    _lib = lib
+    return lib
+
+
+def status_str(rc: int) -> str:
+    return load_library().sa_status_str(rc).decode()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != SA_OK:
+        msg = f"{what}: {status_str(rc)} (status {rc})"
+        if rc == -2:
+            raise NotImplementedError(msg)
+        if rc in (-1, -3):
+            raise ValueError(msg)
+        raise RuntimeError(msg)
+
+
+def _strides(t: torch.Tensor):
+    arr = (ctypes.c_int64 * t.dim())(*t.stride())
+    return arr
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("sparseattention_b200 ops run on CUDA tensors only (no CPU fallback)")
+
+
+# ------------------------------------------------------------------------------- stage 1
+
+def unique_planes(mask: torch.Tensor) -> Tuple[int, int]:
+    B, H = mask.shape[0], mask.shape[1]
+    bu = 1 if (mask.stride(0) == 0 or B == 1) else B
+    hu = 1 if (mask.stride(1) == 0 or H == 1) else H
+    return bu, hu
+
+
+def _canonical_mask(mask: torch.Tensor) -> torch.Tensor:
+    """A view (or, if the layout cannot be streamed with 16-byte loads, a copy) of the
+    mask whose size-1 / broadcast leading dims carry stride 0."""
+    B, H, Sq, Sk = mask.shape
+    bu, hu = unique_planes(mask)
+    base = mask[: bu, : hu]
+    ok = (base.stride(3) == 1 and base.stride(2) % 16 == 0 and base.stride(2) >= Sk
+          and base.data_ptr() % 16 == 0
+          and (bu == 1 or base.stride(0) % 16 == 0) and (hu == 1 or base.stride(1) % 16 == 0))
+    if not ok:
+        base = base.contiguous()
+    return base
+
+
+@torch.library.custom_op("sparseattention_b200::classify_mask", mutates_args=())
+def classify_mask_op(mask: torch.Tensor, block_q: int, block_k: int,
+                     with_bits: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """mask: bool [Bu,Hu,Sq,Sk] holding only the distinct planes.  Returns
+    (full_ids, full_lens, part_ids, part_lens, packed_bits) for those planes."""
+    _require_cuda(mask)
+    if mask.dtype != torch.bool:
+        raise TypeError("mask must be a bool tensor")             # mask_utils.py:18
+    lib = load_library()
+    Bu, Hu, Sq, Sk = mask.shape
+    if Sq % block_q != 0 or Sk % block_k != 0:
+        raise ValueError("Sq and Sk must be multiples of BLOCK_Q and BLOCK_K")   # mask_utils.py:89-90
+    nq, nk = Sq // block_q, Sk // block_k
+    dev = mask.device
+    with torch.cuda.device(dev):
+        full_ids = torch.empty((Bu, Hu, nq, nk), dtype=torch.int32, device=dev)
+        part_ids = torch.empty((Bu, Hu, nq, nk), dtype=torch.int32, device=dev)
+        full_lens = torch.empty((Bu, Hu, nq), dtype=torch.int32, device=dev)
+        part_lens = torch.empty((Bu, Hu, nq), dtype=torch.int32, device=dev)
+        bits = (torch.empty((Bu, Hu, Sk // 32, Sq), dtype=torch.int32, device=dev) if with_bits
+                else torch.empty((0,), dtype=torch.int32, device=dev))
+        ws_bytes = lib.sa_classify_workspace_bytes(Bu, Hu, Sq, Sk)
+        ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
+        sb = mask.stride(0) if Bu > 1 else 0
+        sh = mask.stride(1) if Hu > 1 else 0
+        rc = lib.sa_classify_mask(mask.data_ptr(), sb, sh, mask.stride(2), mask.stride(3),
+                                  Bu, Hu, Sq, Sk, block_q, block_k,
+                                  full_ids.data_ptr(), full_lens.data_ptr(), part_ids.data_ptr(), part_lens.data_ptr(),
+                                  bits.data_ptr() if with_bits else None,
+                                  ws.data_ptr(), ws_bytes, _stream_ptr(dev))
+    _check(rc, "sa_classify_mask")
+    return full_ids, full_lens, part_ids, part_lens, bits
+
+
+@classify_mask_op.register_fake
+def _(mask, block_q, block_k, with_bits):
+    Bu, Hu, Sq, Sk = mask.shape
+    nq, nk = Sq // block_q, Sk // block_k
+    ids = lambda: mask.new_empty((Bu, Hu, nq, nk), dtype=torch.int32)
+    lens = lambda: mask.new_empty((Bu, Hu, nq), dtype=torch.int32)
+    bits = mask.new_empty((Bu, Hu, Sk // 32, Sq) if with_bits else (0,), dtype=torch.int32)
+    return ids(), lens(), ids(), lens(), bits
+
+
+def classify(mask: torch.Tensor, block_q: int, block_k: int, with_bits: bool = True):
+    """Classifies a [B,H,Sq,Sk] bool mask (broadcast dims allowed).  Returns the five
+    tensors of :func:`classify_mask_op` computed over the distinct planes only."""
+    if mask.dim() != 4:
+        raise ValueError("mask must be [B,H,Sq,Sk]")
+    return classify_mask_op(_canonical_mask(mask), int(block_q), int(block_k), bool(with_bits))
+
+
+# ------------------------------------------------------------------------------- stage 2
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """Q/K/V as the kernels want them: unit stride in D; otherwise a contiguous copy."""
+    if t.stride(-1) != 1:
+        return t.contiguous()
+    return t
+
+
+@torch.library.custom_op("sparseattention_b200::attn_fwd", mutates_args=())
+def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, bits: torch.Tensor,
+                full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
+                block_q: int, block_k: int, impl: int, check_status: bool) -> torch.Tensor:
+    """Block-sparse attention forward over precomputed lists.  ``mask`` [B,H,Sq,Sk] and the
+    list tensors ([B,H,nq,nk] / [B,H,nq]) may be expanded views; ``bits`` is the packed plane
+    [Bu,Hu,Sk/32,Sq] (or an empty tensor when absent)."""
+    _require_cuda(q, k, v, mask, full_ids, full_lens, part_ids, part_lens)
+    lib = load_library()
+    B, H, Sq, D = q.shape
+    Sk = k.shape[-2]
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share one of float32 / float16 / bfloat16")
+    if tuple(k.shape) != (B, H, Sk, D) or tuple(v.shape) != (B, H, Sk, D):
+        raise ValueError("k and v must be [B,H,Sk,D] with the batch and head counts of q")
+    if tuple(mask.shape) != (B, H, Sq, Sk):
+        raise ValueError("mask must be (expandable to) [B,H,Sq,Sk]")
+    if Sq % block_q != 0 or Sk % block_k != 0:
+        raise ValueError("Sq and Sk must be multiples of BLOCK_Q and BLOCK_K")
+    scale_log2 = D ** -0.5 / math.log(2)                        # sparse_attn_kernel.py:152
+    dev = q.device
+    with torch.cuda.device(dev):
+        o = torch.empty((B, H, Sq, D), dtype=q.dtype, device=dev)    # sparse_attn_kernel.py:165
+        has_bits = bits.numel() > 0
+        if has_bits:
+            bsb = bits.stride(0) if bits.shape[0] > 1 else 0
+            bsh = bits.stride(1) if bits.shape[1] > 1 else 0
+        else:
+            bsb = bsh = 0
+        status = torch.zeros((1,), dtype=torch.int32, device=dev) if check_status else None
+        rc = lib.sa_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                             _strides(q), _strides(k), _strides(v), _strides(o),
+                             _DTYPES[q.dtype], B, H, Sq, Sk, D, block_q, block_k,
+                             mask.data_ptr(), _strides(mask),
+                             bits.data_ptr() if has_bits else None, bsb, bsh,
+                             full_ids.data_ptr(), _strides(full_ids), full_lens.data_ptr(), _strides(full_lens),
+                             part_ids.data_ptr(), _strides(part_ids), part_lens.data_ptr(), _strides(part_lens),
+                             scale_log2, impl, status.data_ptr() if check_status else None, _stream_ptr(dev))
+    _check(rc, "sa_attn_fwd")
+    if check_status:
+        code = int(status.item())
+        if code != SA_DEV_OK:
+            raise RuntimeError({SA_DEV_WAIT_EXPIRED: "attention kernel: a bounded device-side wait expired",
+                                SA_DEV_BAD_INDEX: "attention kernel: kv-block id out of range in a list"}.get(
+                                    code, f"attention kernel: device status {code}"))
+    return o
+
+
+@attn_fwd_op.register_fake
+def _(q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, block_k, impl, check_status):
+    return q.new_empty(q.shape)
+
+
+def uses_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q: int, block_k: int,
+                 has_bits: bool = True) -> bool:
+    """Whether ``impl='auto'`` runs the tcgen05 kernel for these tensors."""
+    lib = load_library()
+    if q.dtype not in _DTYPES:
+        return False
+    return bool(lib.sa_attn_uses_tcgen05(_DTYPES[q.dtype], q.shape[-1], block_q, block_k, q.shape[-2], k.shape[-2],
+                                         q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                         _strides(q), _strides(k), _strides(v), int(has_bits)))

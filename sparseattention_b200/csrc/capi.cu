@@ -1,0 +1,158 @@
+// extern "C" entry points declared in include/sa_b200.h: argument validation and dispatch.
+#include <cstring>
+
+#include "sa_common.cuh"
+
+namespace {
+
+bool positive(int x) { return x > 0; }
+
+void copy_n(int64_t* dst, const int64_t* src, int n) {
+  for (int i = 0; i < n; ++i) dst[i] = src[i];
+}
+
+}  // namespace
+
+extern "C" {
+
+int sa_abi_version(void) { return SA_ABI_VERSION; }
+
+const char* sa_status_str(int status) {
+  switch (status) {
+    case SA_OK: return "ok";
+    case SA_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case SA_ERR_UNSUPPORTED: return "unsupported shape, dtype or layout";
+    case SA_ERR_WORKSPACE: return "workspace missing or too small";
+    case SA_ERR_CUDA: return "CUDA call failed";
+    case SA_ERR_NO_DEVICE: return "no usable device";
+    default: return "unknown status";
+  }
+}
+
+int sa_unique_planes(int B, int H, int64_t stride_b, int64_t stride_h, int* Bu, int* Hu) {
+  if (!positive(B) || !positive(H) || Bu == nullptr || Hu == nullptr) return SA_ERR_INVALID_ARGUMENT;
+  *Bu = (stride_b == 0) ? 1 : B;
+  *Hu = (stride_h == 0) ? 1 : H;
+  return SA_OK;
+}
+
+size_t sa_classify_workspace_bytes(int Bu, int Hu, int Sq, int Sk) {
+  if (!positive(Bu) || !positive(Hu) || !positive(Sq) || !positive(Sk)) return 0;
+  const size_t cells = static_cast<size_t>(Bu) * Hu * (Sq / sa::kCell) * (Sk / sa::kCell);
+  return (cells + 255) & ~static_cast<size_t>(255);
+}
+
+int sa_classify_mask(const uint8_t* mask,
+                     int64_t stride_b, int64_t stride_h, int64_t stride_q, int64_t stride_k,
+                     int B, int H, int Sq, int Sk, int BLOCK_Q, int BLOCK_K,
+                     int32_t* full_ids, int32_t* full_lens,
+                     int32_t* part_ids, int32_t* part_lens,
+                     uint32_t* packed_bits,
+                     void* workspace, size_t workspace_bytes,
+                     void* stream) {
+  if (mask == nullptr || full_ids == nullptr || full_lens == nullptr || part_ids == nullptr || part_lens == nullptr)
+    return SA_ERR_INVALID_ARGUMENT;
+  if (!positive(B) || !positive(H) || !positive(Sq) || !positive(Sk) || !positive(BLOCK_Q) || !positive(BLOCK_K))
+    return SA_ERR_INVALID_ARGUMENT;
+  if (Sq % BLOCK_Q != 0 || Sk % BLOCK_K != 0) return SA_ERR_INVALID_ARGUMENT;        // mask_utils.py:89-90
+  if (BLOCK_Q % sa::kCell != 0 || BLOCK_K % sa::kCell != 0) return SA_ERR_UNSUPPORTED;
+  if (stride_k != 1 || stride_q < Sk || stride_q % 16 != 0 || stride_b % 16 != 0 || stride_h % 16 != 0 ||
+      stride_b < 0 || stride_h < 0 || reinterpret_cast<uintptr_t>(mask) % 16 != 0)
+    return SA_ERR_UNSUPPORTED;
+  if (packed_bits != nullptr && reinterpret_cast<uintptr_t>(packed_bits) % 16 != 0) return SA_ERR_UNSUPPORTED;
+  int Bu = 1, Hu = 1;
+  sa_unique_planes(B, H, stride_b, stride_h, &Bu, &Hu);
+  const size_t need = sa_classify_workspace_bytes(Bu, Hu, Sq, Sk);
+  if (workspace == nullptr || workspace_bytes < need) return SA_ERR_WORKSPACE;
+
+  sa::ClassifyParams p;
+  p.mask = mask;
+  p.stride_b = stride_b; p.stride_h = stride_h; p.stride_q = stride_q;
+  p.Bu = Bu; p.Hu = Hu; p.Sq = Sq; p.Sk = Sk; p.BQ = BLOCK_Q; p.BK = BLOCK_K;
+  p.cells = static_cast<uint8_t*>(workspace);
+  p.bits = packed_bits;
+  p.full_ids = full_ids; p.full_lens = full_lens; p.part_ids = part_ids; p.part_lens = part_lens;
+  return sa::launch_classify(p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
+}
+
+static int fill_attn_params(sa::AttnParams& p,
+                            const void* q, const void* k, const void* v, void* o,
+                            const int64_t* q_strides, const int64_t* k_strides,
+                            const int64_t* v_strides, const int64_t* o_strides,
+                            int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K) {
+  if (q == nullptr || k == nullptr || v == nullptr || q_strides == nullptr || k_strides == nullptr ||
+      v_strides == nullptr)
+    return SA_ERR_INVALID_ARGUMENT;
+  if (!positive(B) || !positive(H) || !positive(Sq) || !positive(Sk) || !positive(D) || !positive(BLOCK_Q) ||
+      !positive(BLOCK_K))
+    return SA_ERR_INVALID_ARGUMENT;
+  if (Sq % BLOCK_Q != 0 || Sk % BLOCK_K != 0) return SA_ERR_INVALID_ARGUMENT;
+  if (dtype != SA_DTYPE_F32 && dtype != SA_DTYPE_F16 && dtype != SA_DTYPE_BF16) return SA_ERR_UNSUPPORTED;
+  std::memset(&p, 0, sizeof(p));
+  p.q = q; p.k = k; p.v = v; p.o = o;
+  copy_n(p.qs, q_strides, 4); copy_n(p.ks, k_strides, 4); copy_n(p.vs, v_strides, 4);
+  if (o_strides != nullptr) copy_n(p.os, o_strides, 4);
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.D = D; p.BQ = BLOCK_Q; p.BK = BLOCK_K; p.dtype = dtype;
+  return SA_OK;
+}
+
+int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int Sk,
+                         const void* q, const void* k, const void* v,
+                         const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                         int has_packed_bits) {
+  sa::AttnParams p;
+  if (fill_attn_params(p, q, k, v, nullptr, q_strides, k_strides, v_strides, nullptr, dtype, 1, 1, Sq, Sk, D,
+                       BLOCK_Q, BLOCK_K) != SA_OK)
+    return 0;
+  // output layout and bit-plane alignment are checked at launch; assume a fresh contiguous output here
+  static const uint32_t aligned_dummy[4] __attribute__((aligned(16))) = {0, 0, 0, 0};
+  p.bits = has_packed_bits ? aligned_dummy : nullptr;
+  p.o = const_cast<uint32_t*>(aligned_dummy);
+  p.os[3] = 1; p.os[2] = D; p.os[1] = static_cast<int64_t>(D) * Sq; p.os[0] = p.os[1];
+  p.scale_log2 = 1.f;
+  return sa::attn_tc_supported(p);
+}
+
+int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
+                const int64_t* q_strides, const int64_t* k_strides,
+                const int64_t* v_strides, const int64_t* o_strides,
+                int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
+                const uint8_t* mask, const int64_t* mask_strides,
+                const uint32_t* packed_bits, int64_t bits_stride_b, int64_t bits_stride_h,
+                const int32_t* full_ids, const int64_t* full_ids_strides,
+                const int32_t* full_lens, const int64_t* full_lens_strides,
+                const int32_t* part_ids, const int64_t* part_ids_strides,
+                const int32_t* part_lens, const int64_t* part_lens_strides,
+                float scale_log2, int impl, int32_t* dev_status, void* stream) {
+  sa::AttnParams p;
+  if (o == nullptr || o_strides == nullptr) return SA_ERR_INVALID_ARGUMENT;
+  int rc = fill_attn_params(p, q, k, v, o, q_strides, k_strides, v_strides, o_strides, dtype, B, H, Sq, Sk, D,
+                            BLOCK_Q, BLOCK_K);
+  if (rc != SA_OK) return rc;
+  if (full_ids == nullptr || full_lens == nullptr || part_ids == nullptr || part_lens == nullptr ||
+      full_ids_strides == nullptr || full_lens_strides == nullptr || part_ids_strides == nullptr ||
+      part_lens_strides == nullptr)
+    return SA_ERR_INVALID_ARGUMENT;
+  if (impl != SA_IMPL_AUTO && impl != SA_IMPL_SIMT && impl != SA_IMPL_TCGEN05) return SA_ERR_INVALID_ARGUMENT;
+  p.mask = mask;
+  if (mask_strides != nullptr) copy_n(p.ms, mask_strides, 4);
+  p.bits = packed_bits; p.bits_sb = bits_stride_b; p.bits_sh = bits_stride_h;
+  p.full_ids = full_ids; copy_n(p.fis, full_ids_strides, 4);
+  p.full_lens = full_lens; copy_n(p.fls, full_lens_strides, 3);
+  p.part_ids = part_ids; copy_n(p.pis, part_ids_strides, 4);
+  p.part_lens = part_lens; copy_n(p.pls, part_lens_strides, 3);
+  p.scale_log2 = scale_log2;
+  p.dev_status = dev_status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  const bool tc_ok = sa::attn_tc_supported(p) != 0;
+  if (impl == SA_IMPL_TCGEN05 || (impl == SA_IMPL_AUTO && tc_ok)) return sa::launch_attn_tc(p, s);
+
+  // generic kernel
+  if (mask == nullptr || mask_strides == nullptr) return SA_ERR_INVALID_ARGUMENT;
+  if (BLOCK_Q % 32 != 0 || BLOCK_K % 32 != 0) return SA_ERR_UNSUPPORTED;
+  if (D != 16 && D != 32 && D != 64 && D != 128) return SA_ERR_UNSUPPORTED;
+  return sa::launch_attn_simt(p, s) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,181 @@
+// Stage 1: block classifier for a dense boolean attention mask (HBM-bound).
+//
+// Replaces sparseattention/mask_utils.py:47-107 (_compute_mask_inner + its launcher).
+// The reference walks the kv blocks of one query block serially in one program and
+// re-reads an expanded mask once per head; here every distinct mask byte is read
+// exactly once with 16-byte loads:
+//
+//   cells kernel   one warp per 32-row x 512-column strip: each lane streams 32 rows of
+//                  16 bytes, reduces them to "any / all" flags of the 32x32 cells (a lane
+//                  pair per cell) and, optionally, emits the packed bit-plane stage 2 reads.
+//   lists kernel   one warp per (mask plane, query block): folds the cell flags of each
+//                  BLOCK_Q x BLOCK_K tile, ballots the full / partial predicates over 32
+//                  tiles at a time and writes the ascending id lists by a popcount
+//                  prefix (order of mask_utils.py:66-79), tails filled with -1.
+#include "sa_common.cuh"
+
+namespace sa {
+namespace {
+
+__device__ __forceinline__ uint4 ld_stream_16(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// 4 mask bytes -> 4 bits (bit i = byte i non-zero).
+__device__ __forceinline__ uint32_t nibble_of(uint32_t w) {
+  uint32_t nz = (((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) >> 7;
+  nz &= 0x01010101u;
+  return (nz * 0x01020408u) >> 24;   // gathers bits 0,8,16,24 into bits 0..3
+}
+
+__device__ __forceinline__ uint32_t half_word_of(const uint4& v) {
+  return nibble_of(v.x) | (nibble_of(v.y) << 4) | (nibble_of(v.z) << 8) | (nibble_of(v.w) << 12);
+}
+
+constexpr int kCellsThreads = 256;
+
+__global__ void __launch_bounds__(kCellsThreads)
+classify_cells_kernel(const ClassifyParams p, const int chunks_per_row, const long long n_strips) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (static_cast<long long>(blockIdx.x) * kCellsThreads + threadIdx.x) >> 5;
+  const long long n_warps = (static_cast<long long>(gridDim.x) * kCellsThreads) >> 5;
+  const int row_cells = p.Sq / kCell;
+  const int col_cells = p.Sk / kCell;
+  const int odd = lane & 1;
+
+  for (long long strip = warp0; strip < n_strips; strip += n_warps) {
+    const int chunk = static_cast<int>(strip % chunks_per_row);
+    const long long t = strip / chunks_per_row;
+    const int rc = static_cast<int>(t % row_cells);
+    const int plane = static_cast<int>(t / row_cells);
+    const int b = plane / p.Hu, h = plane % p.Hu;
+    const int col = chunk * kStripBytes + lane * 16;
+    const bool active = col < p.Sk;
+    const uint8_t* base = p.mask + b * p.stride_b + h * p.stride_h +
+                          static_cast<int64_t>(rc) * kCell * p.stride_q + col;
+
+    uint32_t and_acc = 0xffffu, or_acc = 0u;
+    uint32_t keep[16];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint4 v[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        v[r] = active ? ld_stream_16(base + static_cast<int64_t>(g * 8 + r) * p.stride_q)
+                      : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int row = g * 8 + r;
+        const uint32_t hb = half_word_of(v[r]);
+        and_acc &= hb;
+        or_acc |= hb;
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, hb, 1);
+        const uint32_t word = odd ? (other | (hb << 16)) : (hb | (other << 16));
+        // even lanes keep rows 0..15 of the cell, odd lanes rows 16..31
+        if ((row >> 4) == 0) { if (!odd) keep[row & 15] = word; }
+        else                 { if (odd)  keep[row & 15] = word; }
+      }
+    }
+    const uint32_t and_all = and_acc & __shfl_xor_sync(0xffffffffu, and_acc, 1);
+    const uint32_t or_any = or_acc | __shfl_xor_sync(0xffffffffu, or_acc, 1);
+    if (active) {
+      const int kb = chunk * (kStripBytes / kCell) + (lane >> 1);
+      if (!odd) {
+        const uint8_t flag = static_cast<uint8_t>((or_any != 0u ? 1u : 0u) | (and_all == 0xffffu ? 2u : 0u));
+        p.cells[(static_cast<int64_t>(plane) * row_cells + rc) * col_cells + kb] = flag;
+      }
+      if (p.bits != nullptr) {
+        uint4* dst = reinterpret_cast<uint4*>(
+            p.bits + (static_cast<int64_t>(plane) * col_cells + kb) * p.Sq + rc * kCell + odd * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          dst[i] = make_uint4(keep[4 * i], keep[4 * i + 1], keep[4 * i + 2], keep[4 * i + 3]);
+      }
+    }
+  }
+}
+
+constexpr int kListsThreads = 128;
+
+__global__ void __launch_bounds__(kListsThreads)
+compact_lists_kernel(const ClassifyParams p, const int n_rows) {
+  const int lane = threadIdx.x & 31;
+  const int row = (blockIdx.x * kListsThreads + threadIdx.x) >> 5;   // (plane, query block)
+  if (row >= n_rows) return;
+  const int nq = p.Sq / p.BQ, nk = p.Sk / p.BK;
+  const int rq = p.BQ / kCell, rk = p.BK / kCell;
+  const int row_cells = p.Sq / kCell, col_cells = p.Sk / kCell;
+  const int plane = row / nq, i = row % nq;
+  const uint8_t* cells = p.cells + (static_cast<int64_t>(plane) * row_cells + static_cast<int64_t>(i) * rq) * col_cells;
+  int32_t* f_out = p.full_ids + static_cast<int64_t>(row) * nk;
+  int32_t* p_out = p.part_ids + static_cast<int64_t>(row) * nk;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  int nf = 0, np = 0;
+  for (int j0 = 0; j0 < nk; j0 += 32) {
+    const int j = j0 + lane;
+    uint32_t any = 0u, all = 2u;
+    if (j < nk) {
+      for (int y = 0; y < rq; ++y) {
+        const uint8_t* c = cells + static_cast<int64_t>(y) * col_cells + static_cast<int64_t>(j) * rk;
+        for (int x = 0; x < rk; ++x) {
+          const uint32_t f = c[x];
+          any |= f;
+          all &= f;
+        }
+      }
+    }
+    const bool is_full = (j < nk) && (all & 2u);                 // count == BQ*BK  (mask_utils.py:72)
+    const bool is_part = (j < nk) && !is_full && (any & 1u);     // 0 < count       (mask_utils.py:76)
+    const uint32_t bf = __ballot_sync(0xffffffffu, is_full);
+    const uint32_t bp = __ballot_sync(0xffffffffu, is_part);
+    if (is_full) f_out[nf + __popc(bf & lt_mask)] = j;
+    if (is_part) p_out[np + __popc(bp & lt_mask)] = j;
+    nf += __popc(bf);
+    np += __popc(bp);
+  }
+  for (int t = nf + lane; t < nk; t += 32) f_out[t] = -1;
+  for (int t = np + lane; t < nk; t += 32) p_out[t] = -1;
+  if (lane == 0) {
+    p.full_lens[row] = nf;                                       // mask_utils.py:81
+    p.part_lens[row] = np;                                       // mask_utils.py:82
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_classify(const ClassifyParams& p, cudaStream_t stream) {
+  const int planes = p.Bu * p.Hu;
+  const int chunks = (p.Sk + kStripBytes - 1) / kStripBytes;
+  const long long n_strips = static_cast<long long>(planes) * (p.Sq / kCell) * chunks;
+  static int sm_count = 0, cells_occ = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    int sms = 0, occ = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, classify_cells_kernel, kCellsThreads, 0);
+    if (e != cudaSuccess) return e;
+    cells_occ = occ > 0 ? occ : 1;
+    sm_count = sms;
+  }
+  const long long warps_per_cta = kCellsThreads / 32;
+  long long ctas = (n_strips + warps_per_cta - 1) / warps_per_cta;
+  const long long resident = static_cast<long long>(sm_count) * cells_occ;
+  if (ctas > resident) ctas = resident;      // persistent: each warp strides over the strips
+  if (ctas < 1) ctas = 1;
+  classify_cells_kernel<<<static_cast<unsigned>(ctas), kCellsThreads, 0, stream>>>(p, chunks, n_strips);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int n_rows = planes * (p.Sq / p.BQ);
+  const int ctas2 = (n_rows * 32 + kListsThreads - 1) / kListsThreads;
+  compact_lists_kernel<<<ctas2, kListsThreads, 0, stream>>>(p, n_rows);
+  return cudaGetLastError();
+}
+
+}  // namespace sa
