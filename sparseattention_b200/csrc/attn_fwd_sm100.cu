@@ -143,6 +143,7 @@ attn_fwd_tc_kernel(const AttnParams p,
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
+    __syncwarp();
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -397,7 +398,10 @@ attn_fwd_tc_kernel(const AttnParams p,
   // ------------------------------------------------------------------ teardown
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 0) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
   if (threadIdx.x == 0 && *abort_flag != 0 && p.dev_status != nullptr)
     atomicMax(p.dev_status, SA_DEV_WAIT_EXPIRED);
 }

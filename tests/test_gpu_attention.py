@@ -1,0 +1,171 @@
+"""Stage 2 on the GPU against the CPU oracle (torch SDPA with the bool mask on the host,
+the reference's own ground truth) and against the recorded outputs of the reference kernel."""
+import numpy as np
+import pytest
+import torch
+
+import sparseattention_b200 as sa
+from oracle import attention as oa
+from oracle import classifier as oc
+from sparseattention_b200 import _native, workloads
+from _util import assert_close_attn, sdpa_cpu, MAX_ABS_16
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _run(q, k, v, mask, bq, bk, impl="auto", md=None):
+    out = sa.sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), bq, bk, mask_metadata=md,
+                              impl=impl, check_status=True)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("bq,bk", [(128, 32), (32, 128), (32, 32), (64, 64)])
+def test_correctness_config_fp32(native_lib, bq, bk):
+    """B=1, H=4, S=512, D=64, fp32 inputs, 32x32-block mask with p=0.5: the CPU-runnable case."""
+    cfg = workloads.CONFIGS["correctness"]
+    q, k, v = workloads.make_qkv(cfg.B, cfg.H, cfg.S, cfg.D, torch.float32, seed=1)
+    mask = workloads.make_mask(cfg, seed=1)
+    ref = sdpa_cpu(q, k, v, mask)
+    out = _run(q, k, v, mask, bq, bk)
+    assert out.dtype == torch.float32 and out.shape == q.shape
+    assert_close_attn(out, ref, torch.float32, f"fp32 ({bq},{bk})")
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,bk", [(128, 32), (128, 64), (128, 128), (64, 32), (64, 128)])
+def test_half_precision_vs_sdpa(native_lib, impl, dtype, D, bk):
+    B, H, S = 2, 2, 512
+    q, k, v = workloads.make_qkv(B, H, S, D, dtype, seed=D + bk)
+    mask = workloads.random_block_mask(B, S, 0.5, 0.15, seed=bk)
+    ref = sdpa_cpu(q, k, v, mask)
+    assert _native.uses_tcgen05(q.to(DEV), k.to(DEV), v.to(DEV), 128, bk)
+    out = _run(q, k, v, mask, 128, bk, impl=impl)
+    assert out.dtype == dtype
+    assert_close_attn(out, ref, dtype, f"{impl} {dtype} D={D} bk={bk}")
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+def test_golden_reference_outputs(golden, native_lib, impl):
+    """fp16 inputs of the recorded cases: equal to the reference kernel on its finite rows,
+    to SDPA on all rows, 0 where a row has no attended key."""
+    q, k, v = (torch.from_numpy(x) for x in (golden.q, golden.k, golden.v))     # fp16, D=64
+    for name, kind, bq, bk in golden.cases:
+        if impl == "tcgen05" and bq != 128:
+            continue
+        mask = torch.from_numpy(golden.mask(kind))
+        out = _run(q, k, v, mask, bq, bk, impl=impl).float().cpu()
+        ref = torch.from_numpy(golden.get(f"{name}/attn_out"))
+        fin = ~torch.isnan(ref).any(-1)
+        assert (out[fin] - ref[fin]).abs().max().item() <= MAX_ABS_16, name
+        assert_close_attn(out, sdpa_cpu(q, k, v, mask), torch.float16, name)
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+def test_masked_rows_empty_blocks_and_dense(native_lib, impl):
+    B, H, S, D = 1, 2, 512, 128
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=3)
+    mask = workloads.random_block_mask(B, S, 0.6, 0.3, seed=3)
+    mask[0, 0, 5] = False                 # a fully masked row inside a live query block
+    mask[0, 0, 128:256] = False           # a query block with both lists empty
+    mask[0, 0, 256:384, :] = False
+    mask[0, 0, 256:384, 32:64] = True     # a query block with exactly one full tile
+    out = _run(q, k, v, mask, 128, 32, impl=impl)
+    assert_close_attn(out, sdpa_cpu(q, k, v, mask), torch.bfloat16, "edge rows")
+    o = out.float().cpu()
+    assert bool((o[:, :, 5] == 0).all()) and bool((o[:, :, 128:256] == 0).all())
+    dense = torch.ones((1, 1, S, S), dtype=torch.bool)
+    out = _run(q, k, v, dense, 128, 32, impl=impl)
+    assert_close_attn(out, sdpa_cpu(q, k, v, dense), torch.bfloat16, "dense")
+    causal = torch.tril(torch.ones((S, S), dtype=torch.bool))[None, None]
+    for bk in (32, 64, 128):
+        out = _run(q, k, v, causal, 128, bk, impl=impl)
+        assert_close_attn(out, sdpa_cpu(q, k, v, causal), torch.bfloat16, f"causal bk={bk}")
+
+
+def test_list_lengths_not_multiple_of_step(native_lib):
+    """Query blocks whose full / partial counts leave ragged 128-row steps (1..7 listed blocks)."""
+    B, H, S, D = 1, 1, 1024, 128
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=9)
+    mask = torch.zeros((1, 1, S, S), dtype=torch.bool)
+    g = torch.Generator().manual_seed(9)
+    for i in range(8):                       # query block i: i+1 listed blocks, first (i+1)//2 full
+        rows = slice(128 * i, 128 * (i + 1))
+        cols = torch.randperm(32, generator=g)[: i + 1]
+        for n, c in enumerate(cols.tolist()):
+            if n < (i + 1) // 2:
+                mask[0, 0, rows, 32 * c:32 * c + 32] = True
+            else:
+                mask[0, 0, rows, 32 * c:32 * c + 32] = torch.rand((128, 32), generator=g) < 0.5
+    ref = sdpa_cpu(q, k, v, mask)
+    for impl in ("simt", "tcgen05"):
+        out = _run(q, k, v, mask, 128, 32, impl=impl)
+        assert_close_attn(out, ref, torch.bfloat16, impl)
+
+
+def test_strided_inputs_and_broadcast_mask(native_lib):
+    B, H, S, D = 2, 3, 256, 128
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn((B, S, 3, H, D), generator=g).to(torch.bfloat16).to(DEV)   # packed projection layout
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))               # [B,H,S,D] views
+    assert not q.is_contiguous()
+    mask = workloads.composed_mask(S, prefix=64, window=96, drop_p=0.2, seed=5)  # [1,1,S,S]
+    ref = sdpa_cpu(q, k, v, mask)
+    for impl in ("simt", "tcgen05"):
+        out = _run(q, k, v, mask, 128, 32, impl=impl)
+        assert_close_attn(out, ref, torch.bfloat16, impl)
+
+
+def test_caller_supplied_metadata(native_lib):
+    """Lists built elsewhere (here: by compute_mask_slow on the GPU, int32, no packed plane) are honoured."""
+    B, H, S, D = 1, 2, 512, 128
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.float16, seed=6)
+    mask = workloads.random_block_mask(B, S, 0.5, 0.2, seed=6).to(DEV)
+    md = sa.compute_mask_slow(mask.expand(B, H, S, S), 128, 32)
+    assert md.packed_bits is None
+    ref = sdpa_cpu(q, k, v, mask)
+    out = _run(q, k, v, mask, 128, 32, md=md)
+    assert_close_attn(out, ref, torch.float16, "metadata from compute_mask_slow")
+    md2 = sa.compute_mask_kernel(mask.expand(B, H, S, S), 128, 32)
+    out2 = _run(q, k, v, mask, 128, 32, md=md2)
+    assert torch.equal(out, out2)
+
+
+def test_deterministic_and_no_unwritten_rows(native_lib):
+    B, H, S, D = 2, 4, 1024, 128
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=7)
+    mask = workloads.document_causal_mask(B, S, (100, 400), 0.1, seed=7)
+    a = _run(q, k, v, mask, 128, 32, impl="tcgen05")
+    b = _run(q, k, v, mask, 128, 32, impl="tcgen05")
+    assert torch.equal(a, b)
+    assert_close_attn(a, sdpa_cpu(q, k, v, mask), torch.bfloat16, "document")
+
+
+def test_unsupported_calls_raise(native_lib):
+    q = torch.randn((1, 1, 128, 48), device=DEV, dtype=torch.bfloat16)
+    mask = torch.ones((1, 1, 128, 128), dtype=torch.bool, device=DEV)
+    with pytest.raises(NotImplementedError):
+        sa.sparse_attention(q, q, q, mask, 128, 32)                 # head dim 48
+    q = torch.randn((1, 1, 128, 64), device=DEV, dtype=torch.float32)
+    with pytest.raises(NotImplementedError):
+        sa.sparse_attention(q, q, q, mask, 128, 32, impl="tcgen05")  # fp32 has no tensor-core path
+    with pytest.raises(TypeError):
+        sa.sparse_attention(q.double(), q.double(), q.double(), mask, 128, 32)
+
+
+def test_headline_shape_slice(native_lib):
+    """One batch element of the headline shape (H=32, S=4096, D=128, bf16, p=0.5): the GPU kernels
+    against each other over all heads, and against host SDPA on two heads."""
+    H, S, D = 32, 4096, 128
+    q, k, v = workloads.make_qkv(1, H, S, D, torch.bfloat16, seed=8, device=DEV)
+    mask = workloads.random_block_mask(1, S, 0.5, 0.1, seed=8, device=DEV)
+    md = sa.compute_mask_kernel(mask.expand(1, H, S, S), 128, 32)
+    out = sa.sparse_attention(q, k, v, mask, 128, 32, mask_metadata=md, impl="tcgen05", check_status=True)
+    hs = [0, 31]
+    ref = sdpa_cpu(q[:, hs], k[:, hs], v[:, hs], mask)
+    assert_close_attn(out[:, hs], ref, torch.bfloat16, "headline slice vs SDPA")
+    simt = sa.sparse_attention(q, k, v, mask, 128, 32, mask_metadata=md, impl="simt", check_status=True)
+    d = (out.float() - simt.float()).abs()
+    assert d.max().item() <= MAX_ABS_16 and d.mean().item() <= 2e-3
