@@ -190,9 +190,10 @@ def run_ours(args):
     _native.load_library()        # fail loudly if the CUDA library is missing
 
     cfg = workloads.CONFIGS["headline"]
-    B, H, S, D = cfg.B, cfg.H, cfg.S, cfg.D
-    ps = list(cfg.drop_ps)
+    B, H, S, D = (args.batch or cfg.B), cfg.H, cfg.S, cfg.D
+    ps = [float(x) for x in args.ps.split(",")] if args.ps else list(cfg.drop_ps)
     dtype = torch.bfloat16
+    warmup = args.warmup if args.profile else max(args.warmup, 3)
     q, k, v = workloads.make_qkv(B, H, S, D, dtype, seed=1000 + rank, device=dev)
     masks = [workloads.random_block_mask(B, S, p, cfg.partial_frac, seed=2000 + 17 * rank + i, device=dev)
              for i, p in enumerate(ps)]
@@ -237,7 +238,7 @@ def run_ours(args):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
     barrier()
     sampler = ClockSampler(local)
@@ -257,6 +258,12 @@ def run_ours(args):
     att_ms = [statistics.mean(ev[s][2 * i + 1].elapsed_time(ev[s][2 * i + 2]) for s in range(args.steps)) for i in range(n_p)]
 
     # ---- end to end through the public entry points with host buffers
+    if args.profile:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "classify_ms": cls_ms, "attn_ms": att_ms, "B": B, "ps": ps}))
+        return
     host_q, host_k, host_v = (t.cpu().pin_memory() for t in (q, k, v))
     host_masks = [m.cpu().pin_memory() for m in masks]
     host_o = torch.empty((B, H, S, D), dtype=dtype).pin_memory()
@@ -302,7 +309,7 @@ def run_ours(args):
         cls_gbs = sum(bytes_p) / (cls_total_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(), "l2": "inputs larger than L2 (Q,K,V 768 MiB, each mask 128 MiB)",
                        "flop_accounting": "4*D*BQ*BK per listed (non-skipped) tile, both stages timed",
@@ -339,6 +346,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-heads", type=int, default=4, help="heads in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiling run: kernels only (no end-to-end leg, no CPU baseline, no warm-up floor)")
+    ap.add_argument("--batch", type=int, default=0, help="profiling: override the batch size of the workload")
+    ap.add_argument("--ps", default="", help="profiling: comma-separated subset of the drop probabilities")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
