@@ -37,7 +37,7 @@ namespace {
 
 constexpr int kTileM = 128;          // query rows per CTA (= BLOCK_Q)
 constexpr int kTileN = 128;          // kv rows per MMA step
-constexpr int kThreadsTC = 192;
+constexpr int kThreadsTC = 320;         // producer warp, MMA warp, 8 softmax warps
 constexpr uint32_t kTmemCols = 256;  // S/P: columns [0,128), O: [128, 128+D)
 constexpr uint32_t kPanelBytes = 128u * 128u;   // 128 rows x 64 elements x 2 B
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
@@ -56,7 +56,8 @@ struct Smem {
   static constexpr uint32_t off_bits = 3 * kTileBytes;          // [2 stages][4 sub-slots][128 rows] u32
   static constexpr uint32_t off_bar = off_bits + 2 * 4 * 128 * 4;
   static constexpr uint32_t off_misc = off_bar + 8 * 16;
-  static constexpr uint32_t total = off_misc + 16;
+  static constexpr uint32_t off_xch = off_misc + 16;             // [2 parities][2 halves][128 rows] f32
+  static constexpr uint32_t total = off_xch + 2 * 2 * 128 * 4;
   static constexpr uint32_t dynamic_bytes = total + 1024;       // slack to align the base to 1024 B
 };
 
@@ -82,6 +83,72 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+
+// One pass over this thread's 64 score columns (two TMEM loads of 32): x = s*scale - m_ref,
+// masked columns -> -inf, P = exp2(x) rounded to T and written over the first 32 columns of the
+// thread's own score range, fp32 row sum of the unrounded P (lines 54, 57, 61) and max of x.
+template <typename T, bool kMasked>
+__device__ __forceinline__ void softmax_pass(uint32_t t_half, float scale, float m_ref, uint32_t w0, uint32_t w1,
+                                             float& sum_out, float& xmax_out) {
+  uint32_t r0[32], r1[32];
+  ptx::tmem_ld32(t_half, r0);
+  ptx::tmem_ld32(t_half + 32, r1);
+  ptx::tmem_ld_wait();
+  const uint64_t scale2 = ptx::pack_f32x2(scale, scale);
+  const uint64_t nm2 = ptx::pack_f32x2(-m_ref, -m_ref);
+  uint64_t sum2 = ptx::pack_f32x2(0.f, 0.f);
+  float xmax = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t a = c == 0 ? r0[2 * i] : r1[2 * i];
+      const uint32_t b = c == 0 ? r0[2 * i + 1] : r1[2 * i + 1];
+      float x0, x1;
+      ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_u32x2(a, b), scale2, nm2), x0, x1);
+      if (kMasked) {
+        const uint32_t w = c == 0 ? w0 : w1;
+        x0 = (w >> (2 * i)) & 1u ? x0 : -INFINITY;                 // line 47
+        x1 = (w >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
+      }
+      xmax = ptx::max3(xmax, x0, x1);
+      const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+      sum2 = ptx::add_f32x2(sum2, ptx::pack_f32x2(p0, p1));
+      pk[i] = Fmt<T>::pack2(p0, p1);
+    }
+    ptx::tmem_st16(t_half + c * 16, pk);
+  }
+  float s0, s1;
+  ptx::unpack_f32x2(sum2, s0, s1);
+  sum_out = s0 + s1;
+  xmax_out = xmax;
+}
+
+// Max of the raw (masked) scores of this thread's 64 columns.
+template <bool kMasked>
+__device__ __forceinline__ void max_pass(uint32_t t_half, uint32_t w0, uint32_t w1, float& smax_out) {
+  uint32_t r0[32], r1[32];
+  ptx::tmem_ld32(t_half, r0);
+  ptx::tmem_ld32(t_half + 32, r1);
+  ptx::tmem_ld_wait();
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
+    float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
+    if (kMasked) {
+      a0 = (w0 >> (2 * i)) & 1u ? a0 : -INFINITY;
+      a1 = (w0 >> (2 * i + 1)) & 1u ? a1 : -INFINITY;
+      b0 = (w1 >> (2 * i)) & 1u ? b0 : -INFINITY;
+      b1 = (w1 >> (2 * i + 1)) & 1u ? b1 : -INFINITY;
+    }
+    mx = ptx::max3(mx, a0, a1);
+    mx = ptx::max3(mx, b0, b1);
+  }
+  smax_out = mx;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreadsTC, 2)
 attn_fwd_tc_kernel(const AttnParams p,
@@ -98,6 +165,7 @@ attn_fwd_tc_kernel(const AttnParams p,
   auto bar = [&](int i) { return sbase + L::off_bar + 8u * static_cast<uint32_t>(i); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
+  float* xch = reinterpret_cast<float*>(smem + L::off_xch);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblk = blockIdx.x;
@@ -119,9 +187,9 @@ attn_fwd_tc_kernel(const AttnParams p,
   if (total == 0) {                     // nothing attended: rows are 0, no tensor memory needed
     if (warp >= 2) {
       const int row = (warp & 3) * 32 + lane;
-      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2]);
+      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / 2) * ((warp - 2) >> 2));
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+      for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
     }
     return;
   }
@@ -133,12 +201,12 @@ attn_fwd_tc_kernel(const AttnParams p,
     ptx::mbar_init(bar(BAR_V_FULL), 1);
     ptx::mbar_init(bar(BAR_V_EMPTY), 1);
     ptx::mbar_init(bar(BAR_S_FULL), 1);
-    ptx::mbar_init(bar(BAR_P_FULL), 128);
+    ptx::mbar_init(bar(BAR_P_FULL), 256);
     ptx::mbar_init(bar(BAR_O_FULL), 1);
     ptx::mbar_init(bar(BAR_BITS_FULL0), 1);
     ptx::mbar_init(bar(BAR_BITS_FULL1), 1);
-    ptx::mbar_init(bar(BAR_BITS_EMPTY0), 128);
-    ptx::mbar_init(bar(BAR_BITS_EMPTY1), 128);
+    ptx::mbar_init(bar(BAR_BITS_EMPTY0), 256);
+    ptx::mbar_init(bar(BAR_BITS_EMPTY1), 256);
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -271,7 +339,7 @@ attn_fwd_tc_kernel(const AttnParams p,
         ptx::tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kTileN / 16; ++kk) {                 // O += P.V   (line 61)
-          ptx::mma_ts(tO, tS + kk * 8u, ptx::umma_desc_sw128(sV + kk * 2048u, kPanelBytes),
+          ptx::mma_ts(tO, tS + (kk / 4) * 64u + (kk % 4) * 8u, ptx::umma_desc_sw128(sV + kk * 2048u, kPanelBytes),
                       idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
         ptx::mma_commit(bar(BAR_V_EMPTY));
@@ -280,12 +348,17 @@ attn_fwd_tc_kernel(const AttnParams p,
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ softmax (thread = row)
-    const int lq = warp & 3;                       // TMEM lane quarter this warp may access
+    // ------------------------------------------------------------------ softmax
+    // Thread = (query row, half of the 128 score columns).  Warps 2-5 take columns 0-63,
+    // warps 6-9 columns 64-127; a warp may only touch the TMEM lanes of its quarter (warp % 4).
+    const int lq = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = lq * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(lq * 32) << 16;
+    const uint32_t tS_half = tS + lane_off + 64u * half;      // this half's scores; its P goes to the first 32 columns
+    const uint32_t tO_half = tO + lane_off + (D / 2) * half;  // this half's share of the O columns
     const float scale = p.scale_log2;
-    float m = -INFINITY, l = 0.f;                  // lines 103-104
+    float m = -INFINITY, l = 0.f;                  // lines 103-104; l holds this half's partial sum
     bool ok = true;
     for (int j = 0; j < n_steps; ++j) {
       ok = ptx::mbar_wait(bar(BAR_S_FULL), j & 1, abort_flag);
@@ -293,78 +366,71 @@ attn_fwd_tc_kernel(const AttnParams p,
       if (!ok) break;
       ptx::tc_fence_after();
       const bool masked = j >= n_plain;
-      uint32_t w[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+      uint32_t w0 = 0xffffffffu, w1 = 0xffffffffu;
       if (masked) {
         const int u = j - n_plain, st = u & 1;
         ok = ptx::mbar_wait(bar(BAR_BITS_FULL0 + st), (u >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int e = j * eps + c / sps;
-          w[c] = e < n_full ? 0xffffffffu : (e < total ? bits_smem[(st * 4 + c) * 128 + row] : 0u);
-        }
+        const int c0 = 2 * half, c1 = 2 * half + 1;
+        const int e0 = j * eps + c0 / sps, e1 = j * eps + c1 / sps;
+        w0 = e0 < n_full ? 0xffffffffu : (e0 < total ? bits_smem[(st * 4 + c0) * 128 + row] : 0u);
+        w1 = e1 < n_full ? 0xffffffffu : (e1 < total ? bits_smem[(st * 4 + c1) * 128 + row] : 0u);
         ptx::mbar_arrive(bar(BAR_BITS_EMPTY0 + st));
       }
-      // pass 1: row maximum of the (masked) scores
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(tS + lane_off + c * 32, r);
-        ptx::tmem_ld_wait();
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            mx = fmaxf(mx, (w[c] >> i) & 1u ? __uint_as_float(r[i]) : -INFINITY);   // line 47
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        }
-      }
-      const float m_tile = mx * scale;                                               // lines 48 / 50
-      const float m_cand = fmaxf(m, m_tile);
-      float m_new, alpha;
-      if (m == -INFINITY) { m_new = m_cand; alpha = 1.f; }                 // nothing accumulated yet
-      else if (m_cand > m + kRescaleThreshold) { m_new = m_cand; alpha = ex2_approx(m - m_new); }  // line 55
-      else { m_new = m; alpha = 1.f; }                                     // keep the older reference point
-      const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;              // guard the reference lacks (line 53)
+      float* xch_mine = xch + ((j & 1) * 2 + half) * 128 + row;
+      const float* xch_other = xch + ((j & 1) * 2 + (half ^ 1)) * 128 + row;
 
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {                // acc *= alpha (line 58)
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld32(tO + lane_off + c * 32, r);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          ptx::tmem_st32(tO + lane_off + c * 32, r);
+      // Rows that already hold a finite running max exponentiate against it straight away
+      // (one pass); the max only moves when a score exceeds it by more than the threshold.
+      const bool slow = __any_sync(0xffffffffu, m == -INFINITY);
+      float m_new = m, alpha = 1.f, m_ref = m;
+      bool second_pass = true;
+      if (!slow) {
+        float sum, xmax;
+        if (masked) softmax_pass<T, true>(tS_half, scale, m, w0, w1, sum, xmax);
+        else        softmax_pass<T, false>(tS_half, scale, m, w0, w1, sum, xmax);
+        *xch_mine = xmax;
+        ptx::named_bar_sync(1 + lq, 64);
+        const float xrow = fmaxf(xmax, *xch_other);
+        if (!__any_sync(0xffffffffu, xrow > kRescaleThreshold)) {
+          l += sum;
+          second_pass = false;
+        } else if (xrow > kRescaleThreshold) {
+          m_new = m + xrow;
+          alpha = ex2_approx(-xrow);                              // exp2(m - m_new), line 55
+          m_ref = m_new;
         }
+      } else {
+        float smax;
+        if (masked) max_pass<true>(tS_half, w0, w1, smax);
+        else        max_pass<false>(tS_half, w0, w1, smax);
+        *xch_mine = smax;
+        ptx::named_bar_sync(1 + lq, 64);
+        const float m_tile = fmaxf(smax, *xch_other) * scale;     // lines 48 / 50
+        const float m_cand = fmaxf(m, m_tile);
+        if (m == -INFINITY) { m_new = m_cand; }                   // nothing accumulated yet
+        else if (m_cand > m + kRescaleThreshold) { m_new = m_cand; alpha = ex2_approx(m - m_new); }
+        m_ref = (m_new == -INFINITY) ? 0.f : m_new;               // guard the reference lacks (line 53)
       }
-      // pass 2: P = exp2(S*scale - m), row sum in fp32 before the cast (lines 54, 57, 61)
-      float row_sum = 0.f;
+      if (second_pass) {
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this half's columns
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(tS + lane_off + c * 32, r);
-        ptx::tmem_ld_wait();
-        uint32_t pk[16];
+          for (int c = 0; c < D / 64; ++c) {
+            uint32_t r[32];
+            ptx::tmem_ld32(tO_half + c * 32, r);
+            ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float x0 = fmaf(__uint_as_float(r[2 * i]), scale, -m_ref);
-          float x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale, -m_ref);
-          if (masked) {
-            x0 = (w[c] >> (2 * i)) & 1u ? x0 : -INFINITY;
-            x1 = (w[c] >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            ptx::tmem_st32(tO_half + c * 32, r);
           }
-          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-          row_sum += p0 + p1;
-          pk[i] = Fmt<T>::pack2(p0, p1);
         }
-        ptx::tmem_st16(tS + lane_off + c * 16, pk);      // P overwrites columns of S already consumed
+        float sum, xmax;
+        if (masked) softmax_pass<T, true>(tS_half, scale, m_ref, w0, w1, sum, xmax);
+        else        softmax_pass<T, false>(tS_half, scale, m_ref, w0, w1, sum, xmax);
+        l = l * alpha + sum;                                      // line 57
+        m = m_new;                                                // line 56
       }
-      l = l * alpha + row_sum;                            // line 57
-      m = m_new;                                          // line 56
       ptx::tmem_st_wait();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(BAR_P_FULL));
@@ -375,12 +441,17 @@ attn_fwd_tc_kernel(const AttnParams p,
     }
     if (ok) {
       ptx::tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;          // line 144, with 0 for an empty row
-      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2]);
+      float* xch_mine = xch + ((n_steps & 1) * 2 + half) * 128 + row;
+      const float* xch_other = xch + ((n_steps & 1) * 2 + (half ^ 1)) * 128 + row;
+      *xch_mine = l;
+      ptx::named_bar_sync(1 + lq, 64);
+      const float l_row = l + *xch_other;
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;          // line 144, with 0 for an empty row
+      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / 2) * half);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
-        ptx::tmem_ld32(tO + lane_off + c * 32, r);
+        ptx::tmem_ld32(tO_half + c * 32, r);
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
