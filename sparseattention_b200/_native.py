@@ -14,7 +14,7 @@ from typing import List, Tuple
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libsparseattn_b200.so")
+LIB_PATH = os.environ.get("SPARSEATTN_B200_LIB") or os.path.join(_PKG_DIR, "libsparseattn_b200.so")
 
 # mirrors of the header's constants
 SA_ABI_VERSION = 1

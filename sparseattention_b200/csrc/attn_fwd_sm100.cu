@@ -3,28 +3,30 @@
 // Replaces sparseattention/sparse_attn_kernel.py:72-146 (kernel) and 10-63 (inner loop)
 // for fp16 / bf16, head dim 64 or 128, BLOCK_Q = 128 and BLOCK_K in {32, 64, 128}.
 //
-// One CTA owns one query block (128 rows) of one (batch, head); two CTAs share an SM so
-// that the tensor pipe of one overlaps the softmax of the other.  Per CTA:
+// One CTA (one per SM, 320 threads) owns one query block (128 rows) of one (batch, head) and
+// walks its two kv-block lists -- the full list first, then the partial list: the order of
+// sparse_attn_kernel.py:113-142 -- in steps of 128 kv rows (128 / BLOCK_K listed blocks):
 //
-//   warp 0    producer.  Reads the two kv-block id lists of the query block (full list first,
-//             then the partial list: the order of sparse_attn_kernel.py:113-142) and, for each
-//             step of 128 kv rows, gathers 128/BLOCK_K listed kv blocks of K and of V into one
-//             128-row, 128-byte-swizzled shared-memory tile with TMA tile loads whose row
-//             coordinate comes from the list, plus the 512-byte bit-mask tiles of the
-//             partial blocks (cp.async.bulk from the packed plane of stage 1).
-//   warp 1    MMA issuer.  S = Q.K^T (tcgen05.mma, both operands in shared memory, fp32
-//             accumulator in tensor memory), then O += P.V with P read from tensor memory.
-//   warps 2-5 softmax, one thread per query row.  Reads S from tensor memory, applies the bit
-//             mask on steps that contain a partial or padding block, keeps the running max /
-//             sum in fp32 in base 2 (scale folded as in sparse_attn_kernel.py:152), writes P
-//             (rounded to the V dtype, line 61) over S in tensor memory, rescales O in tensor
-//             memory only when the running max grew by more than 2^8, and finally writes
-//             O / l.  A row with no attended key yields 0 (the reference yields NaN, line 53).
+//   warp 0    producer.  Reads the lists and, in the order the tensor core will consume them,
+//             gathers the listed kv blocks of K and of V into 128-row, 128-byte-swizzled tiles
+//             of a five-stage shared-memory ring with TMA tile loads whose row coordinate comes
+//             from the list, plus the 512-byte bit-mask tiles of the partial blocks
+//             (cp.async.bulk from the packed plane of stage 1).
+//   warp 1    MMA issuer.  S(j) = Q.K(j)^T into one of two score buffers in tensor memory
+//             (tcgen05.mma, operands in shared memory), always one step ahead of the softmax;
+//             O += P(j).V(j) with P read from tensor memory.
+//   warps 2-9 softmax; a thread owns a query row and one half of the 128 score columns.  Scores
+//             are exponentiated against the row's running max in a single pass (base 2, scale
+//             folded as in sparse_attn_kernel.py:152); the max moves, and O is rescaled in
+//             tensor memory, only when a score exceeds it by more than 2^8.  Steps that contain
+//             a partial or padding block apply the bit mask; steps of full blocks do no mask
+//             work.  P (rounded to the V dtype, line 61) overwrites the head of the thread's own
+//             score columns; row sums stay in fp32 (line 57).  Finally O / l is written; a row
+//             with no attended key yields 0 (the reference yields NaN, line 53).
 //
-// Steps made only of full blocks skip all mask work.  A step whose last slots run past the
-// end of the lists re-loads the first listed block with an all-zero mask word.
-// Every mbarrier wait is bounded; on expiry the CTA reports SA_DEV_WAIT_EXPIRED, frees its
-// tensor memory and returns.
+// A step whose last slots run past the end of the lists re-loads the first listed block with an
+// all-zero mask word.  Every mbarrier wait is bounded; on expiry the CTA reports
+// SA_DEV_WAIT_EXPIRED, frees its tensor memory and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -37,14 +39,28 @@ namespace {
 
 constexpr int kTileM = 128;          // query rows per CTA (= BLOCK_Q)
 constexpr int kTileN = 128;          // kv rows per MMA step
-constexpr int kThreadsTC = 320;         // producer warp, MMA warp, 8 softmax warps
-constexpr uint32_t kTmemCols = 256;  // S/P: columns [0,128), O: [128, 128+D)
+constexpr int kThreadsTC = 384;      // warps: K producer, V producer, S issuer, P.V issuer, 8 softmax
+constexpr int kSoftmaxWarp0 = 4;     // first softmax warp (a multiple of 4: TMEM lane quarter = warp % 4)
+constexpr uint32_t kTmemCols = 512;  // score buffers at columns 0 and 128, O at 256, P buffers at 384 and 448
+constexpr int kStagesK = 3;          // K tiles in flight in shared memory
+constexpr int kStagesV = 2;          // V tiles in flight in shared memory
+constexpr int kBitStages = 4;        // steps of bit-mask tiles in flight
 constexpr uint32_t kPanelBytes = 128u * 128u;   // 128 rows x 64 elements x 2 B
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 
 enum Bar : int {
-  BAR_Q = 0, BAR_K_FULL, BAR_K_EMPTY, BAR_V_FULL, BAR_V_EMPTY, BAR_S_FULL, BAR_P_FULL, BAR_O_FULL,
-  BAR_BITS_FULL0, BAR_BITS_FULL1, BAR_BITS_EMPTY0, BAR_BITS_EMPTY1, BAR_COUNT
+  BAR_Q = 0,
+  BAR_K_FULL,                                      // kStagesK: K tile landed
+  BAR_K_EMPTY = BAR_K_FULL + kStagesK,             // kStagesK: K tile consumed by S = Q.K^T
+  BAR_V_FULL = BAR_K_EMPTY + kStagesK,             // kStagesV
+  BAR_V_EMPTY = BAR_V_FULL + kStagesV,             // kStagesV: V tile consumed by O += P.V
+  BAR_S_FULL = BAR_V_EMPTY + kStagesV,             // 2: scores of buffer j & 1 complete
+  BAR_P_FULL = BAR_S_FULL + 2,                     // 2: P of buffer j & 1 written (and S read) by all 256 softmax threads
+  BAR_PV_DONE = BAR_P_FULL + 2,                    // 2: O += P.V of step j complete (barrier j & 1)
+  BAR_O_FULL = BAR_PV_DONE + 2,                    // last O += P.V complete
+  BAR_BITS_FULL,                                   // kBitStages
+  BAR_BITS_EMPTY = BAR_BITS_FULL + kBitStages,
+  BAR_COUNT = BAR_BITS_EMPTY + kBitStages
 };
 
 template <int D>
@@ -52,14 +68,19 @@ struct Smem {
   static constexpr uint32_t kTileBytes = kPanelBytes * (D / 64);
   static constexpr uint32_t off_q = 0;
   static constexpr uint32_t off_k = kTileBytes;
-  static constexpr uint32_t off_v = 2 * kTileBytes;
-  static constexpr uint32_t off_bits = 3 * kTileBytes;          // [2 stages][4 sub-slots][128 rows] u32
-  static constexpr uint32_t off_bar = off_bits + 2 * 4 * 128 * 4;
-  static constexpr uint32_t off_misc = off_bar + 8 * 16;
+  static constexpr uint32_t off_v = off_k + kStagesK * kTileBytes;
+  static constexpr uint32_t off_bits = off_v + kStagesV * kTileBytes;      // [kBitStages][4 sub-slots][128 rows] u32
+  static constexpr uint32_t off_bar = off_bits + kBitStages * 4 * 128 * 4;
+  static constexpr uint32_t off_misc = off_bar + 8 * 32;
   static constexpr uint32_t off_xch = off_misc + 16;             // [2 parities][2 halves][128 rows] f32
   static constexpr uint32_t total = off_xch + 2 * 2 * 128 * 4;
+#ifdef SA_TRACE
+  static constexpr uint32_t dynamic_bytes = total + 1024 + 5 * 500 * 8;
+#else
   static constexpr uint32_t dynamic_bytes = total + 1024;       // slack to align the base to 1024 B
+#endif
 };
+static_assert(BAR_COUNT <= 32, "barrier area too small");
 
 template <typename T> struct Fmt;
 template <> struct Fmt<__half> {
@@ -77,6 +98,23 @@ template <> struct Fmt<__nv_bfloat16> {
   }
 };
 
+// Developer tracing (compiled out unless SA_TRACE is defined): CTA (0,0) appends
+// (event, step, SM clock) triples per role to a device array read back by sa_debug_read_trace().
+#ifdef SA_TRACE
+constexpr int kTraceCap = 500;                  // events per role, kept in shared memory
+__device__ long long g_trace[5 * 4096];
+#define SA_TRACE_EVENT(role, ev, step)                                                      \
+  do {                                                                                      \
+    if (trace_on && trace_n[role] < kTraceCap) {                                            \
+      trace_buf[(role) * kTraceCap + trace_n[role]++] =                                     \
+          (static_cast<long long>(ev) << 56) | (static_cast<long long>(step) << 40) |       \
+          (clock64() & 0xffffffffffll);                                                     \
+    }                                                                                       \
+  } while (0)
+#else
+#define SA_TRACE_EVENT(role, ev, step) do { } while (0)
+#endif
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -85,10 +123,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 
 
 // One pass over this thread's 64 score columns (two TMEM loads of 32): x = s*scale - m_ref,
-// masked columns -> -inf, P = exp2(x) rounded to T and written over the first 32 columns of the
-// thread's own score range, fp32 row sum of the unrounded P (lines 54, 57, 61) and max of x.
-template <typename T, bool kMasked>
-__device__ __forceinline__ void softmax_pass(uint32_t t_half, float scale, float m_ref, uint32_t w0, uint32_t w1,
+// masked columns -> -inf, P = exp2(x) rounded to T and written to the 32 columns at t_p, fp32 row sum of the unrounded P (lines 54, 57, 61) and max of x.
+template <typename T, bool kMasked, bool kNoExp = false>
+__device__ __forceinline__ void softmax_pass(uint32_t t_half, uint32_t t_p, float scale, float m_ref, uint32_t w0, uint32_t w1,
                                              float& sum_out, float& xmax_out) {
   uint32_t r0[32], r1[32];
   ptx::tmem_ld32(t_half, r0);
@@ -113,11 +150,11 @@ __device__ __forceinline__ void softmax_pass(uint32_t t_half, float scale, float
         x1 = (w >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
       }
       xmax = ptx::max3(xmax, x0, x1);
-      const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+      const float p0 = kNoExp ? x0 * x1 : ex2_approx(x0), p1 = kNoExp ? x1 * x0 : ex2_approx(x1);
       sum2 = ptx::add_f32x2(sum2, ptx::pack_f32x2(p0, p1));
       pk[i] = Fmt<T>::pack2(p0, p1);
     }
-    ptx::tmem_st16(t_half + c * 16, pk);
+    ptx::tmem_st16(t_p + c * 16, pk);
   }
   float s0, s1;
   ptx::unpack_f32x2(sum2, s0, s1);
@@ -150,7 +187,7 @@ __device__ __forceinline__ void max_pass(uint32_t t_half, uint32_t w0, uint32_t 
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kThreadsTC, 2)
+__global__ void __launch_bounds__(kThreadsTC, 1)
 attn_fwd_tc_kernel(const AttnParams p,
                    const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -168,6 +205,12 @@ attn_fwd_tc_kernel(const AttnParams p,
   float* xch = reinterpret_cast<float*>(smem + L::off_xch);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef SA_TRACE
+  const bool trace_on = blockIdx.x == 16 && blockIdx.y == 40;
+  int trace_n[5] = {0, 0, 0, 0, 0};
+  long long* trace_buf = reinterpret_cast<long long*>(smem + L::total);
+  if (trace_on) for (int i = threadIdx.x; i < 5 * kTraceCap; i += blockDim.x) trace_buf[i] = 0;
+#endif
   const int qblk = blockIdx.x;
   const int b = blockIdx.y / p.H, h = blockIdx.y % p.H;
   const int nk = p.Sk / p.BK;
@@ -185,9 +228,9 @@ attn_fwd_tc_kernel(const AttnParams p,
   T* o_base = static_cast<T*>(p.o) + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(qblk) * kTileM * p.os[2];
 
   if (total == 0) {                     // nothing attended: rows are 0, no tensor memory needed
-    if (warp >= 2) {
+    if (warp >= kSoftmaxWarp0) {
       const int row = (warp & 3) * 32 + lane;
-      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / 2) * ((warp - 2) >> 2));
+      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / 2) * ((warp - kSoftmaxWarp0) >> 2));
 #pragma unroll
       for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -196,17 +239,24 @@ attn_fwd_tc_kernel(const AttnParams p,
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(bar(BAR_Q), 1);
-    ptx::mbar_init(bar(BAR_K_FULL), 1);
-    ptx::mbar_init(bar(BAR_K_EMPTY), 1);
-    ptx::mbar_init(bar(BAR_V_FULL), 1);
-    ptx::mbar_init(bar(BAR_V_EMPTY), 1);
-    ptx::mbar_init(bar(BAR_S_FULL), 1);
-    ptx::mbar_init(bar(BAR_P_FULL), 256);
+    for (int i = 0; i < kStagesK; ++i) {
+      ptx::mbar_init(bar(BAR_K_FULL + i), 1);
+      ptx::mbar_init(bar(BAR_K_EMPTY + i), 1);
+    }
+    for (int i = 0; i < kStagesV; ++i) {
+      ptx::mbar_init(bar(BAR_V_FULL + i), 1);
+      ptx::mbar_init(bar(BAR_V_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(bar(BAR_S_FULL + i), 1);
+      ptx::mbar_init(bar(BAR_P_FULL + i), 256);
+      ptx::mbar_init(bar(BAR_PV_DONE + i), 1);
+    }
     ptx::mbar_init(bar(BAR_O_FULL), 1);
-    ptx::mbar_init(bar(BAR_BITS_FULL0), 1);
-    ptx::mbar_init(bar(BAR_BITS_FULL1), 1);
-    ptx::mbar_init(bar(BAR_BITS_EMPTY0), 256);
-    ptx::mbar_init(bar(BAR_BITS_EMPTY1), 256);
+    for (int i = 0; i < kBitStages; ++i) {
+      ptx::mbar_init(bar(BAR_BITS_FULL + i), 1);
+      ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 256);
+    }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -219,131 +269,171 @@ attn_fwd_tc_kernel(const AttnParams p,
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base;
-  const uint32_t tO = tmem_base + 128;
+  const uint32_t tO = tmem_base + 256;   // score buffer s lives at tmem_base + 128 * s, P buffer s at 384 + 64 * s
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ producer
+  if (warp < 2) {
+    // ------------------------------------------------------------------ producers
+    // Warp 0 gathers the K tiles (and the bit-mask tiles), warp 1 the V tiles.  The whole warp
+    // runs the loop: lane 0 waits for a free stage and arms its barrier, lanes 0-7 each issue one
+    // TMA box, lanes 0-3 fetch the list entries of a step.
+    const bool is_k = warp == 0;
+    const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
     if (lane == 0) {
-      ptx::prefetch_tensormap(&tm_q);
-      ptx::prefetch_tensormap(&tm_k);
-      ptx::prefetch_tensormap(&tm_v);
-      const int qb = p.qs[0] ? b : 0, qh = p.qs[1] ? h : 0;
-      const int kb = p.ks[0] ? b : 0, kh = p.ks[1] ? h : 0;
-      const int vb = p.vs[0] ? b : 0, vh = p.vs[1] ? h : 0;
-      ptx::mbar_arrive_expect_tx(bar(BAR_Q), L::kTileBytes);
+      ptx::prefetch_tensormap(tm);
+      if (is_k) {
+        ptx::prefetch_tensormap(&tm_q);
+        const int qb = p.qs[0] ? b : 0, qh = p.qs[1] ? h : 0;
+        ptx::mbar_arrive_expect_tx(bar(BAR_Q), L::kTileBytes);
 #pragma unroll
-      for (int pnl = 0; pnl < D / 64; ++pnl)
-        ptx::tma_load_4d(sQ + pnl * kPanelBytes, &tm_q, bar(BAR_Q), pnl * 64, qblk * kTileM, qh, qb);
-
-      const int32_t* fids = p.full_ids + b * p.fis[0] + h * p.fis[1] + static_cast<int64_t>(qblk) * p.fis[2];
-      const int32_t* pids = p.part_ids + b * p.pis[0] + h * p.pis[1] + static_cast<int64_t>(qblk) * p.pis[2];
-      const uint32_t* bits_plane = p.bits + b * p.bits_sb + h * p.bits_sh;
-      bool bad_index = false;
-      auto entry_id = [&](int e) -> int {
-        const int ee = e < total ? e : 0;         // slots past the end re-load the first listed block
-        int id = ee < n_full ? fids[ee * p.fis[3]] : pids[(ee - n_full) * p.pis[3]];   // line 33
-        if (static_cast<unsigned>(id) >= static_cast<unsigned>(nk)) { bad_index = true; id = 0; }
-        return id;
-      };
-      int nxt[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) nxt[c] = (c < eps) ? entry_id(c) : 0;
-
-      const uint32_t slot_bytes = static_cast<uint32_t>(p.BK) * 128u;
-      bool ok = true;
-      for (int j = 0; j < n_steps; ++j) {
-        int cur[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) cur[c] = nxt[c];
-        if (j + 1 < n_steps) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) nxt[c] = (c < eps) ? entry_id((j + 1) * eps + c) : 0;
-        }
-        // K tile: free once S(j-1) has been computed
-        if (j > 0) ok = ptx::mbar_wait(bar(BAR_K_EMPTY), (j - 1) & 1, abort_flag);
-        if (!ok) break;
-        ptx::mbar_arrive_expect_tx(bar(BAR_K_FULL), L::kTileBytes);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if (c < eps) {
-#pragma unroll
-            for (int pnl = 0; pnl < D / 64; ++pnl)
-              ptx::tma_load_4d(sK + pnl * kPanelBytes + c * slot_bytes, &tm_k, bar(BAR_K_FULL),
-                               pnl * 64, cur[c] * p.BK, kh, kb);
-          }
-        }
-        // bit-mask tiles of the partial blocks of this step
-        if (j >= n_plain) {
-          const int u = j - n_plain, st = u & 1;
-          if (u >= 2) ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY0 + st), ((u >> 1) - 1) & 1, abort_flag);
-          if (!ok) break;
-          int n_tiles = 0;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int e = j * eps + c / sps;
-            n_tiles += (e >= n_full && e < total) ? 1 : 0;
-          }
-          if (n_tiles > 0) ptx::mbar_arrive_expect_tx(bar(BAR_BITS_FULL0 + st), 512u * n_tiles);
-          else ptx::mbar_arrive(bar(BAR_BITS_FULL0 + st));
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int ec = c / sps;
-            const int e = j * eps + ec;
-            if (e >= n_full && e < total) {
-              const int64_t kb32 = static_cast<int64_t>(cur[ec]) * sps + (c % sps);
-              const uint32_t* src = bits_plane + kb32 * p.Sq + qblk * kTileM;
-              ptx::bulk_load(sBits + static_cast<uint32_t>(st * 4 + c) * 512u, src, 512u, bar(BAR_BITS_FULL0 + st));
-            }
-          }
-        }
-        // V tile: free once O += P.V (j-1) has been computed
-        if (j > 0) ok = ptx::mbar_wait(bar(BAR_V_EMPTY), (j - 1) & 1, abort_flag);
-        if (!ok) break;
-        ptx::mbar_arrive_expect_tx(bar(BAR_V_FULL), L::kTileBytes);
+        for (int pnl = 0; pnl < D / 64; ++pnl)
+          ptx::tma_load_4d(sQ + pnl * kPanelBytes, &tm_q, bar(BAR_Q), pnl * 64, qblk * kTileM, qh, qb);
+      }
+    }
+    const int cb = is_k ? (p.ks[0] ? b : 0) : (p.vs[0] ? b : 0);
+    const int ch = is_k ? (p.ks[1] ? h : 0) : (p.vs[1] ? h : 0);
+    const int n_stages = is_k ? kStagesK : kStagesV;
+    const uint32_t s_tiles = is_k ? sK : sV;
+    const int bar_full = is_k ? BAR_K_FULL : BAR_V_FULL, bar_empty = is_k ? BAR_K_EMPTY : BAR_V_EMPTY;
+    const int32_t* fids = p.full_ids + b * p.fis[0] + h * p.fis[1] + static_cast<int64_t>(qblk) * p.fis[2];
+    const int32_t* pids = p.part_ids + b * p.pis[0] + h * p.pis[1] + static_cast<int64_t>(qblk) * p.pis[2];
+    const uint32_t* bits_plane = p.bits + b * p.bits_sb + h * p.bits_sh;
+    bool bad_index = false;
+    // kv-block id of entry `lane` of step j (lanes >= entries per step hold 0)
+    auto my_id_of = [&](int j) -> int {
+      if (lane >= eps || j >= n_steps) return 0;
+      const int e = j * eps + lane;
+      const int ee = e < total ? e : 0;           // slots past the end re-load the first listed block
+      int id = ee < n_full ? fids[ee * p.fis[3]] : pids[(ee - n_full) * p.pis[3]];   // line 33
+      if (static_cast<unsigned>(id) >= static_cast<unsigned>(nk)) { bad_index = true; id = 0; }
+      return id;
+    };
+    const uint32_t slot_bytes = static_cast<uint32_t>(p.BK) * 128u;
+    constexpr int kPanels = D / 64;
+    const int c_of_lane = lane / kPanels, pnl_of_lane = lane % kPanels;
+    bool ok = true;
+    int id_cur = my_id_of(0), id_nxt = my_id_of(1);
+    int st = 0, round = 0;
+    for (int j = 0; j < n_steps && ok; ++j) {
+      const int id_nxt2 = my_id_of(j + 2);            // fetched two steps before it is needed
+      if (lane == 0) SA_TRACE_EVENT(warp, 0, j);
+      const uint32_t dst = s_tiles + st * L::kTileBytes;
+      const uint32_t full_bar = bar(bar_full + st);
+      if (lane == 0) {
+        if (round > 0) ok = ptx::mbar_wait(bar(bar_empty + st), (round - 1) & 1, abort_flag);
+        if (ok) ptx::mbar_arrive_expect_tx(full_bar, (p.debug & 2) ? slot_bytes : L::kTileBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (lane == 0) SA_TRACE_EVENT(warp, 1, j);
+      const int id_c = __shfl_sync(0xffffffffu, id_cur, c_of_lane & 3);
+      if (ok && c_of_lane < eps && (!(p.debug & 2) || lane == 0))
+        ptx::tma_load_4d(dst + pnl_of_lane * kPanelBytes + c_of_lane * slot_bytes, tm, full_bar,
+                         pnl_of_lane * 64, id_c * p.BK, ch, cb);
+      if (lane == 0) SA_TRACE_EVENT(warp, 2, j);
+      if (is_k && j >= n_plain && ok) {               // bit-mask tiles of the partial blocks of step j
+        const int u = j - n_plain, bst = u % kBitStages;
+        int n_tiles = 0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          if (c < eps) {
-#pragma unroll
-            for (int pnl = 0; pnl < D / 64; ++pnl)
-              ptx::tma_load_4d(sV + pnl * kPanelBytes + c * slot_bytes, &tm_v, bar(BAR_V_FULL),
-                               pnl * 64, cur[c] * p.BK, vh, vb);
+          const int e = j * eps + c / sps;
+          n_tiles += (e >= n_full && e < total) ? 1 : 0;
+        }
+        if (lane == 0) {
+          if (u >= kBitStages) ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
+          if (ok) {
+            if (n_tiles > 0) ptx::mbar_arrive_expect_tx(bar(BAR_BITS_FULL + bst), 512u * n_tiles);
+            else ptx::mbar_arrive(bar(BAR_BITS_FULL + bst));
           }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        const int c = lane & 3, ec = c / sps;
+        const int id_b = __shfl_sync(0xffffffffu, id_cur, ec);
+        const int e = j * eps + ec;
+        if (ok && lane < 4 && e >= n_full && e < total) {
+          const int64_t kb32 = static_cast<int64_t>(id_b) * sps + (c % sps);
+          const uint32_t* src = bits_plane + kb32 * p.Sq + qblk * kTileM;
+          ptx::bulk_load(sBits + static_cast<uint32_t>(bst * 4 + c) * 512u, src, 512u, bar(BAR_BITS_FULL + bst));
         }
       }
-      if (bad_index && p.dev_status != nullptr) atomicMax(p.dev_status, SA_DEV_BAD_INDEX);
+      id_cur = id_nxt; id_nxt = id_nxt2;
+      if (++st == n_stages) { st = 0; ++round; }
     }
+    if (is_k && __any_sync(0xffffffffu, bad_index) && lane == 0 && p.dev_status != nullptr)
+      atomicMax(p.dev_status, SA_DEV_BAD_INDEX);
     __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ S issuer: S(j) = Q.K(j)^T  (line 40)
     if (lane == 0) {
       constexpr uint32_t idesc_s = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, kTileN, 0);
-      constexpr uint32_t idesc_o = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, D, 1);
+      const uint64_t dq = ptx::umma_desc_sw128(sQ, 16u);
+      const uint32_t dq_lo = static_cast<uint32_t>(dq), d_hi = static_cast<uint32_t>(dq >> 32);
+      const uint32_t dk_lo0 = static_cast<uint32_t>(ptx::umma_desc_sw128(sK, 16u));
       bool ok = ptx::mbar_wait(bar(BAR_Q), 0, abort_flag);
+      int st = 0, round = 0;
       for (int j = 0; j < n_steps && ok; ++j) {
-        ok = ptx::mbar_wait(bar(BAR_K_FULL), j & 1, abort_flag);
+        SA_TRACE_EVENT(2, 0, j);
+        // the score buffer is free once the softmax of step j-2 has read it
+        if (j >= 2) ok = ptx::mbar_wait(bar(BAR_P_FULL + (j & 1)), ((j - 2) >> 1) & 1, abort_flag);
         if (!ok) break;
+        SA_TRACE_EVENT(2, 1, j);
+        ok = ptx::mbar_wait(bar(BAR_K_FULL + st), round & 1, abort_flag);
+        if (!ok) break;
+        SA_TRACE_EVENT(2, 2, j);
         ptx::tc_fence_after();
+        const uint32_t tS = tmem_base + 128u * (j & 1);
+        const uint32_t dk_lo = dk_lo0 + st * (L::kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {                      // S = Q.K^T  (line 40)
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32u;
-          ptx::mma_ss(tS, ptx::umma_desc_sw128(sQ + off, 16u), ptx::umma_desc_sw128(sK + off, 16u),
-                      idesc_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          constexpr uint32_t kPanelStep = kPanelBytes >> 4;
+          const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
+          if ((p.debug & 4) && kk > 0) break;
+          if (kk == 0) ptx::mma_ss_lo<false>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+          else         ptx::mma_ss_lo<true>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
         }
-        ptx::mma_commit(bar(BAR_K_EMPTY));
-        ptx::mma_commit(bar(BAR_S_FULL));
-        ok = ptx::mbar_wait(bar(BAR_P_FULL), j & 1, abort_flag);
+        SA_TRACE_EVENT(2, 3, j);
+        ptx::mma_commit(bar(BAR_K_EMPTY + st));
+        ptx::mma_commit(bar(BAR_S_FULL + (j & 1)));
+        SA_TRACE_EVENT(2, 4, j);
+        if (++st == kStagesK) { st = 0; ++round; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ P.V issuer: O += P(j).V(j)  (line 61)
+    if (lane == 0) {
+      constexpr uint32_t idesc_o = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, D, 1);
+      const uint64_t dv = ptx::umma_desc_sw128(sV, kPanelBytes);
+      const uint32_t dv_lo0 = static_cast<uint32_t>(dv), dv_hi = static_cast<uint32_t>(dv >> 32);
+      bool ok = true;
+      for (int j = 0; j < n_steps && ok; ++j) {
+        SA_TRACE_EVENT(3, 0, j);
+        ok = ptx::mbar_wait(bar(BAR_P_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
         if (!ok) break;
-        ok = ptx::mbar_wait(bar(BAR_V_FULL), j & 1, abort_flag);
+        SA_TRACE_EVENT(3, 1, j);
+        ok = ptx::mbar_wait(bar(BAR_V_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
         if (!ok) break;
+        SA_TRACE_EVENT(3, 2, j);
         ptx::tc_fence_after();
+        const uint32_t tP = tmem_base + 384u + 64u * (j & 1);
+        const uint32_t dv_lo = dv_lo0 + (j & 1) * (L::kTileBytes >> 4);
+        if (j == 0) {
 #pragma unroll
-        for (int kk = 0; kk < kTileN / 16; ++kk) {                 // O += P.V   (line 61)
-          ptx::mma_ts(tO, tS + (kk / 4) * 64u + (kk % 4) * 8u, ptx::umma_desc_sw128(sV + kk * 2048u, kPanelBytes),
-                      idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kTileN / 16; ++kk) {
+            if ((p.debug & 4) && kk > 0) break;
+            if (kk == 0) ptx::mma_ts_lo<false>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+            else         ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kTileN / 16; ++kk) {
+            if ((p.debug & 4) && kk > 0) break;
+            ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+          }
         }
-        ptx::mma_commit(bar(BAR_V_EMPTY));
+        SA_TRACE_EVENT(3, 3, j);
+        ptx::mma_commit(bar(BAR_V_EMPTY + (j & 1)));
+        ptx::mma_commit(bar(BAR_PV_DONE + (j & 1)));
         if (j == n_steps - 1) ptx::mma_commit(bar(BAR_O_FULL));
+        SA_TRACE_EVENT(3, 4, j);
       }
     }
     __syncwarp();
@@ -352,34 +442,49 @@ attn_fwd_tc_kernel(const AttnParams p,
     // Thread = (query row, half of the 128 score columns).  Warps 2-5 take columns 0-63,
     // warps 6-9 columns 64-127; a warp may only touch the TMEM lanes of its quarter (warp % 4).
     const int lq = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - kSoftmaxWarp0) >> 2;
     const int row = lq * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(lq * 32) << 16;
-    const uint32_t tS_half = tS + lane_off + 64u * half;      // this half's scores; its P goes to the first 32 columns
     const uint32_t tO_half = tO + lane_off + (D / 2) * half;  // this half's share of the O columns
     const float scale = p.scale_log2;
     float m = -INFINITY, l = 0.f;                  // lines 103-104; l holds this half's partial sum
     bool ok = true;
     for (int j = 0; j < n_steps; ++j) {
-      ok = ptx::mbar_wait(bar(BAR_S_FULL), j & 1, abort_flag);
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 0, j);
+      ok = ptx::mbar_wait(bar(BAR_S_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (j >= 2) {     // the P buffer of this step is free once P.V of step j-2 has read it
+        ok = ptx::mbar_wait(bar(BAR_PV_DONE + (j & 1)), ((j - 2) >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 1, j);
       ptx::tc_fence_after();
+      // this half's scores of buffer j & 1, and where its P goes
+      const uint32_t tS_half = tmem_base + 128u * (j & 1) + lane_off + 64u * half;
+      const uint32_t tP_half = tmem_base + 384u + 64u * (j & 1) + lane_off + 32u * half;
       const bool masked = j >= n_plain;
       uint32_t w0 = 0xffffffffu, w1 = 0xffffffffu;
       if (masked) {
-        const int u = j - n_plain, st = u & 1;
-        ok = ptx::mbar_wait(bar(BAR_BITS_FULL0 + st), (u >> 1) & 1, abort_flag);
+        const int u = j - n_plain, st = u % kBitStages;
+        ok = ptx::mbar_wait(bar(BAR_BITS_FULL + st), (u / kBitStages) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const int c0 = 2 * half, c1 = 2 * half + 1;
         const int e0 = j * eps + c0 / sps, e1 = j * eps + c1 / sps;
         w0 = e0 < n_full ? 0xffffffffu : (e0 < total ? bits_smem[(st * 4 + c0) * 128 + row] : 0u);
         w1 = e1 < n_full ? 0xffffffffu : (e1 < total ? bits_smem[(st * 4 + c1) * 128 + row] : 0u);
-        ptx::mbar_arrive(bar(BAR_BITS_EMPTY0 + st));
+        ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
       }
       float* xch_mine = xch + ((j & 1) * 2 + half) * 128 + row;
       const float* xch_other = xch + ((j & 1) * 2 + (half ^ 1)) * 128 + row;
+      if (p.debug & 1) {
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar(BAR_P_FULL + (j & 1)));
+        continue;
+      }
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 2, j);
 
       // Rows that already hold a finite running max exponentiate against it straight away
       // (one pass); the max only moves when a score exceeds it by more than the threshold.
@@ -388,8 +493,9 @@ attn_fwd_tc_kernel(const AttnParams p,
       bool second_pass = true;
       if (!slow) {
         float sum, xmax;
-        if (masked) softmax_pass<T, true>(tS_half, scale, m, w0, w1, sum, xmax);
-        else        softmax_pass<T, false>(tS_half, scale, m, w0, w1, sum, xmax);
+        if (p.debug & 8) softmax_pass<T, true, true>(tS_half, tP_half, scale, m, w0, w1, sum, xmax);
+        else if (masked) softmax_pass<T, true>(tS_half, tP_half, scale, m, w0, w1, sum, xmax);
+        else        softmax_pass<T, false>(tS_half, tP_half, scale, m, w0, w1, sum, xmax);
         *xch_mine = xmax;
         ptx::named_bar_sync(1 + lq, 64);
         const float xrow = fmaxf(xmax, *xch_other);
@@ -415,6 +521,12 @@ attn_fwd_tc_kernel(const AttnParams p,
       }
       if (second_pass) {
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this half's columns
+          // O must hold every product up to step j-1 before it is rescaled.  P.V(j-2) is known to be
+          // complete (waited for above), so this barrier is at most one phase behind.
+          ok = ptx::mbar_wait(bar(BAR_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          ptx::tc_fence_after();
 #pragma unroll
           for (int c = 0; c < D / 64; ++c) {
             uint32_t r[32];
@@ -426,14 +538,16 @@ attn_fwd_tc_kernel(const AttnParams p,
           }
         }
         float sum, xmax;
-        if (masked) softmax_pass<T, true>(tS_half, scale, m_ref, w0, w1, sum, xmax);
-        else        softmax_pass<T, false>(tS_half, scale, m_ref, w0, w1, sum, xmax);
+        if (masked) softmax_pass<T, true>(tS_half, tP_half, scale, m_ref, w0, w1, sum, xmax);
+        else        softmax_pass<T, false>(tS_half, tP_half, scale, m_ref, w0, w1, sum, xmax);
         l = l * alpha + sum;                                      // line 57
         m = m_new;                                                // line 56
       }
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 3, j);
       ptx::tmem_st_wait();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(bar(BAR_P_FULL));
+      ptx::mbar_arrive(bar(BAR_P_FULL + (j & 1)));
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 4, j);
     }
     if (ok) {
       ok = ptx::mbar_wait(bar(BAR_O_FULL), 0, abort_flag);
@@ -475,6 +589,13 @@ attn_fwd_tc_kernel(const AttnParams p,
   }
   if (threadIdx.x == 0 && *abort_flag != 0 && p.dev_status != nullptr)
     atomicMax(p.dev_status, SA_DEV_WAIT_EXPIRED);
+#ifdef SA_TRACE
+  if (trace_on) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 5 * kTraceCap; i += blockDim.x)
+      g_trace[(i / kTraceCap) * 4096 + (i % kTraceCap)] = trace_buf[i];
+  }
+#endif
 }
 
 // ---------------------------------------------------------------------- host side
@@ -554,6 +675,12 @@ int attn_tc_supported(const AttnParams& p) {
     return 0;
   return 1;
 }
+
+#ifdef SA_TRACE
+extern "C" int sa_debug_read_trace(long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n));
+}
+#endif
 
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
   if (!attn_tc_supported(p)) return SA_ERR_UNSUPPORTED;

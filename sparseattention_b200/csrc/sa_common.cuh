@@ -41,6 +41,7 @@ struct AttnParams {
   int dtype;
   float scale_log2;
   int32_t* dev_status;
+  int debug;
 };
 
 cudaError_t launch_attn_simt(const AttnParams& p, cudaStream_t stream);
