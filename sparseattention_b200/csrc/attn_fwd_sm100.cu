@@ -39,7 +39,11 @@ namespace {
 
 constexpr int kTileM = 128;          // query rows per CTA (= BLOCK_Q)
 constexpr int kTileN = 128;          // kv rows per MMA step
-constexpr int kThreadsTC = 384;      // warps: K producer, V producer, S issuer, P.V issuer, 8 softmax
+#ifndef SA_SOFTMAX_SPLIT
+#define SA_SOFTMAX_SPLIT 2
+#endif
+constexpr int kSplit = SA_SOFTMAX_SPLIT;      // threads per query row in the softmax (2 or 4 column groups)
+constexpr int kThreadsTC = 128 + 128 * kSplit;   // warps: K producer, V producer, S issuer, P.V issuer, 4 * kSplit softmax
 constexpr int kSoftmaxWarp0 = 4;     // first softmax warp (a multiple of 4: TMEM lane quarter = warp % 4)
 constexpr uint32_t kTmemCols = 512;  // score buffers at columns 0 and 128, O at 256, P buffers at 384 and 448
 constexpr int kStagesK = 3;          // K tiles in flight in shared memory
@@ -47,6 +51,14 @@ constexpr int kStagesV = 2;          // V tiles in flight in shared memory
 constexpr int kBitStages = 4;        // steps of bit-mask tiles in flight
 constexpr uint32_t kPanelBytes = 128u * 128u;   // 128 rows x 64 elements x 2 B
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
+#ifndef SA_POLY_PLAIN
+#define SA_POLY_PLAIN 0
+#endif
+#ifndef SA_POLY_MASKED
+#define SA_POLY_MASKED 0
+#endif
+// every n-th pair of scores is exponentiated on the FMA pipe instead of the MUFU (0 = none)
+constexpr int kPolyPlain = SA_POLY_PLAIN, kPolyMasked = SA_POLY_MASKED;
 
 enum Bar : int {
   BAR_Q = 0,
@@ -55,7 +67,7 @@ enum Bar : int {
   BAR_V_FULL = BAR_K_EMPTY + kStagesK,             // kStagesV
   BAR_V_EMPTY = BAR_V_FULL + kStagesV,             // kStagesV: V tile consumed by O += P.V
   BAR_S_FULL = BAR_V_EMPTY + kStagesV,             // 2: scores of buffer j & 1 complete
-  BAR_P_FULL = BAR_S_FULL + 2,                     // 2: P of buffer j & 1 written (and S read) by all 256 softmax threads
+  BAR_P_FULL = BAR_S_FULL + 2,                     // 2: P of buffer j & 1 written (and S read) by all softmax threads
   BAR_PV_DONE = BAR_P_FULL + 2,                    // 2: O += P.V of step j complete (barrier j & 1)
   BAR_O_FULL = BAR_PV_DONE + 2,                    // last O += P.V complete
   BAR_BITS_FULL,                                   // kBitStages
@@ -72,8 +84,8 @@ struct Smem {
   static constexpr uint32_t off_bits = off_v + kStagesV * kTileBytes;      // [kBitStages][4 sub-slots][128 rows] u32
   static constexpr uint32_t off_bar = off_bits + kBitStages * 4 * 128 * 4;
   static constexpr uint32_t off_misc = off_bar + 8 * 32;
-  static constexpr uint32_t off_xch = off_misc + 16;             // [2 parities][2 halves][128 rows] f32
-  static constexpr uint32_t total = off_xch + 2 * 2 * 128 * 4;
+  static constexpr uint32_t off_xch = off_misc + 16;             // [2 parities][kSplit column groups][128 rows] f32
+  static constexpr uint32_t total = off_xch + 2 * kSplit * 128 * 4;
 #ifdef SA_TRACE
   static constexpr uint32_t dynamic_bytes = total + 1024 + 5 * 500 * 8;
 #else
@@ -122,39 +134,42 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 
-// One pass over this thread's 64 score columns (two TMEM loads of 32): x = s*scale - m_ref,
-// masked columns -> -inf, P = exp2(x) rounded to T and written to the 32 columns at t_p, fp32 row sum of the unrounded P (lines 54, 57, 61) and max of x.
-template <typename T, bool kMasked, bool kNoExp = false>
-__device__ __forceinline__ void softmax_pass(uint32_t t_half, uint32_t t_p, float scale, float m_ref, uint32_t w0, uint32_t w1,
-                                             float& sum_out, float& xmax_out) {
-  uint32_t r0[32], r1[32];
-  ptx::tmem_ld32(t_half, r0);
-  ptx::tmem_ld32(t_half + 32, r1);
+// One pass over this thread's kCW score columns (kCW / 32 TMEM loads): x = s*scale - m_ref, masked
+// columns -> -inf, P = exp2(x) rounded to T and written to the kCW / 2 columns at t_p, fp32 row sum
+// of the unrounded P (lines 54, 57, 61) and max of x.  w[c] is the bit-mask word of columns 32c..32c+31.
+template <typename T, bool kMasked, int kPolyEvery, int kCW, bool kNoExp = false>
+__device__ __forceinline__ void softmax_pass(uint32_t t_s, uint32_t t_p, float scale, float m_ref,
+                                             const uint32_t (&w)[kCW / 32], float& sum_out, float& xmax_out) {
+  constexpr int kChunks = kCW / 32;
+  uint32_t r[kChunks][32];
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) ptx::tmem_ld32(t_s + 32 * c, r[c]);
   ptx::tmem_ld_wait();
   const uint64_t scale2 = ptx::pack_f32x2(scale, scale);
   const uint64_t nm2 = ptx::pack_f32x2(-m_ref, -m_ref);
   uint64_t sum2 = ptx::pack_f32x2(0.f, 0.f);
   float xmax = -INFINITY;
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int c = 0; c < kChunks; ++c) {
     uint32_t pk[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const uint32_t a = c == 0 ? r0[2 * i] : r1[2 * i];
-      const uint32_t b = c == 0 ? r0[2 * i + 1] : r1[2 * i + 1];
       float x0, x1;
-      ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_u32x2(a, b), scale2, nm2), x0, x1);
+      ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_u32x2(r[c][2 * i], r[c][2 * i + 1]), scale2, nm2), x0, x1);
       if (kMasked) {
-        const uint32_t w = c == 0 ? w0 : w1;
-        x0 = (w >> (2 * i)) & 1u ? x0 : -INFINITY;                 // line 47
-        x1 = (w >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
+        x0 = (w[c] >> (2 * i)) & 1u ? x0 : -INFINITY;                 // line 47
+        x1 = (w[c] >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
       }
       xmax = ptx::max3(xmax, x0, x1);
-      const float p0 = kNoExp ? x0 * x1 : ex2_approx(x0), p1 = kNoExp ? x1 * x0 : ex2_approx(x1);
+      float p0, p1;
+      if (kNoExp) { p0 = x0 * x1; p1 = x1 * x0; }
+      else if (kPolyEvery > 0 && ((c * 16 + i) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1)
+        ptx::exp2_poly_pair(x0, x1, p0, p1);
+      else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
       sum2 = ptx::add_f32x2(sum2, ptx::pack_f32x2(p0, p1));
       pk[i] = Fmt<T>::pack2(p0, p1);
     }
-    ptx::tmem_st16(t_p + c * 16, pk);
+    ptx::tmem_st16(t_p + 16 * c, pk);
   }
   float s0, s1;
   ptx::unpack_f32x2(sum2, s0, s1);
@@ -162,28 +177,37 @@ __device__ __forceinline__ void softmax_pass(uint32_t t_half, uint32_t t_p, floa
   xmax_out = xmax;
 }
 
-// Max of the raw (masked) scores of this thread's 64 columns.
-template <bool kMasked>
-__device__ __forceinline__ void max_pass(uint32_t t_half, uint32_t w0, uint32_t w1, float& smax_out) {
-  uint32_t r0[32], r1[32];
-  ptx::tmem_ld32(t_half, r0);
-  ptx::tmem_ld32(t_half + 32, r1);
-  ptx::tmem_ld_wait();
+// Max of the raw (masked) scores of this thread's kCW columns.
+template <bool kMasked, int kCW>
+__device__ __forceinline__ void max_pass(uint32_t t_s, const uint32_t (&w)[kCW / 32], float& smax_out) {
+  constexpr int kChunks = kCW / 32;
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    float a0 = __uint_as_float(r0[2 * i]), a1 = __uint_as_float(r0[2 * i + 1]);
-    float b0 = __uint_as_float(r1[2 * i]), b1 = __uint_as_float(r1[2 * i + 1]);
-    if (kMasked) {
-      a0 = (w0 >> (2 * i)) & 1u ? a0 : -INFINITY;
-      a1 = (w0 >> (2 * i + 1)) & 1u ? a1 : -INFINITY;
-      b0 = (w1 >> (2 * i)) & 1u ? b0 : -INFINITY;
-      b1 = (w1 >> (2 * i + 1)) & 1u ? b1 : -INFINITY;
+  for (int c = 0; c < kChunks; ++c) {
+    uint32_t r[32];
+    ptx::tmem_ld32(t_s + 32 * c, r);
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float a0 = __uint_as_float(r[2 * i]), a1 = __uint_as_float(r[2 * i + 1]);
+      if (kMasked) {
+        a0 = (w[c] >> (2 * i)) & 1u ? a0 : -INFINITY;
+        a1 = (w[c] >> (2 * i + 1)) & 1u ? a1 : -INFINITY;
+      }
+      mx = ptx::max3(mx, a0, a1);
     }
-    mx = ptx::max3(mx, a0, a1);
-    mx = ptx::max3(mx, b0, b1);
   }
   smax_out = mx;
+}
+
+// Moves kCols fp32 columns between tensor memory and registers (kCols = 32 or 16).
+template <int kCols>
+__device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&r)[kCols]) {
+  if constexpr (kCols == 32) ptx::tmem_ld32(taddr, r); else ptx::tmem_ld16(taddr, r);
+}
+template <int kCols>
+__device__ __forceinline__ void tmem_store_cols(uint32_t taddr, const uint32_t (&r)[kCols]) {
+  if constexpr (kCols == 32) ptx::tmem_st32(taddr, r); else ptx::tmem_st16(taddr, r);
 }
 
 template <typename T, int D>
@@ -230,9 +254,9 @@ attn_fwd_tc_kernel(const AttnParams p,
   if (total == 0) {                     // nothing attended: rows are 0, no tensor memory needed
     if (warp >= kSoftmaxWarp0) {
       const int row = (warp & 3) * 32 + lane;
-      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / 2) * ((warp - kSoftmaxWarp0) >> 2));
+      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / kSplit) * ((warp - kSoftmaxWarp0) >> 2));
 #pragma unroll
-      for (int i = 0; i < D / 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+      for (int i = 0; i < D / (8 * kSplit); ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
     }
     return;
   }
@@ -249,13 +273,13 @@ attn_fwd_tc_kernel(const AttnParams p,
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(bar(BAR_S_FULL + i), 1);
-      ptx::mbar_init(bar(BAR_P_FULL + i), 256);
+      ptx::mbar_init(bar(BAR_P_FULL + i), 128 * kSplit);
       ptx::mbar_init(bar(BAR_PV_DONE + i), 1);
     }
     ptx::mbar_init(bar(BAR_O_FULL), 1);
     for (int i = 0; i < kBitStages; ++i) {
       ptx::mbar_init(bar(BAR_BITS_FULL + i), 1);
-      ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 256);
+      ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 128 * kSplit);
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -371,8 +395,10 @@ attn_fwd_tc_kernel(const AttnParams p,
       int st = 0, round = 0;
       for (int j = 0; j < n_steps && ok; ++j) {
         SA_TRACE_EVENT(2, 0, j);
-        // the score buffer is free once the softmax of step j-2 has read it
-        if (j >= 2) ok = ptx::mbar_wait(bar(BAR_P_FULL + (j & 1)), ((j - 2) >> 1) & 1, abort_flag);
+        // Buffer j & 1 is reused: its scores were read by the softmax of step j-2 and its P by
+        // O += P.V of step j-2.  The latter implies the former, and having it complete before S(j)
+        // lets the softmax of step j write P without a wait of its own.
+        if (j >= 2) ok = ptx::mbar_wait(bar(BAR_PV_DONE + (j & 1)), ((j - 2) >> 1) & 1, abort_flag);
         if (!ok) break;
         SA_TRACE_EVENT(2, 1, j);
         ok = ptx::mbar_wait(bar(BAR_K_FULL + st), round & 1, abort_flag);
@@ -439,46 +465,51 @@ attn_fwd_tc_kernel(const AttnParams p,
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax
-    // Thread = (query row, half of the 128 score columns).  Warps 2-5 take columns 0-63,
-    // warps 6-9 columns 64-127; a warp may only touch the TMEM lanes of its quarter (warp % 4).
+    // Thread = (query row, one of kSplit groups of 128 / kSplit score columns): the first four
+    // softmax warps take the first group, the next four the second, ...; a warp may only touch the
+    // TMEM lanes of its quarter (warp % 4).  A group is kCW / 32 sub-slots, one bit-mask word each.
+    constexpr int kCW = kTileN / kSplit;           // score columns per thread
+    constexpr int kOC = D / kSplit;                // O columns this thread rescales and stores
+    constexpr int kOChunk = kOC > 32 ? 32 : kOC;
     const int lq = warp & 3;
-    const int half = (warp - kSoftmaxWarp0) >> 2;
+    const int quarter = (warp - kSoftmaxWarp0) >> 2;
     const int row = lq * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(lq * 32) << 16;
-    const uint32_t tO_half = tO + lane_off + (D / 2) * half;  // this half's share of the O columns
+    const uint32_t tO_mine = tO + lane_off + kOC * quarter;
     const float scale = p.scale_log2;
-    float m = -INFINITY, l = 0.f;                  // lines 103-104; l holds this half's partial sum
-    bool ok = true;
+    float m = -INFINITY, l = 0.f;                  // lines 103-104; l holds this quarter's partial sum
+    bool all_finite = false;                       // every row of the warp holds a finite running max
     for (int j = 0; j < n_steps; ++j) {
       if (threadIdx.x == 128) SA_TRACE_EVENT(4, 0, j);
-      ok = ptx::mbar_wait(bar(BAR_S_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      if (j >= 2) {     // the P buffer of this step is free once P.V of step j-2 has read it
-        ok = ptx::mbar_wait(bar(BAR_PV_DONE + (j & 1)), ((j - 2) >> 1) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
+      ptx::mbar_wait(bar(BAR_S_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
       if (threadIdx.x == 128) SA_TRACE_EVENT(4, 1, j);
       ptx::tc_fence_after();
-      // this half's scores of buffer j & 1, and where its P goes
-      const uint32_t tS_half = tmem_base + 128u * (j & 1) + lane_off + 64u * half;
-      const uint32_t tP_half = tmem_base + 384u + 64u * (j & 1) + lane_off + 32u * half;
+      // this quarter's scores of buffer j & 1, and where its P goes
+      const uint32_t tS_mine = tmem_base + 128u * (j & 1) + lane_off + kCW * quarter;
+      const uint32_t tP_mine = tmem_base + 384u + 64u * (j & 1) + lane_off + (kCW / 2) * quarter;
       const bool masked = j >= n_plain;
-      uint32_t w0 = 0xffffffffu, w1 = 0xffffffffu;
+      uint32_t w[kCW / 32];
+#pragma unroll
+      for (int c = 0; c < kCW / 32; ++c) w[c] = 0xffffffffu;
       if (masked) {
         const int u = j - n_plain, st = u % kBitStages;
-        ok = ptx::mbar_wait(bar(BAR_BITS_FULL + st), (u / kBitStages) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const int c0 = 2 * half, c1 = 2 * half + 1;
-        const int e0 = j * eps + c0 / sps, e1 = j * eps + c1 / sps;
-        w0 = e0 < n_full ? 0xffffffffu : (e0 < total ? bits_smem[(st * 4 + c0) * 128 + row] : 0u);
-        w1 = e1 < n_full ? 0xffffffffu : (e1 < total ? bits_smem[(st * 4 + c1) * 128 + row] : 0u);
+        ptx::mbar_wait(bar(BAR_BITS_FULL + st), (u / kBitStages) & 1, abort_flag);
+#pragma unroll
+        for (int c = 0; c < kCW / 32; ++c) {
+          const int ss = quarter * (kCW / 32) + c;           // sub-slot of the step
+          const int e = j * eps + ss / sps;
+          w[c] = e < n_full ? 0xffffffffu : (e < total ? bits_smem[(st * 4 + ss) * 128 + row] : 0u);
+        }
         ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
       }
-      float* xch_mine = xch + ((j & 1) * 2 + half) * 128 + row;
-      const float* xch_other = xch + ((j & 1) * 2 + (half ^ 1)) * 128 + row;
+      float* xch_mine = xch + ((j & 1) * kSplit + quarter) * 128 + row;
+      const float* xch_row = xch + (j & 1) * kSplit * 128 + row;
+      auto row_max = [&]() {
+        float v = xch_row[0];
+#pragma unroll
+        for (int g = 1; g < kSplit; ++g) v = fmaxf(v, xch_row[128 * g]);
+        return v;
+      };
       if (p.debug & 1) {
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar(BAR_P_FULL + (j & 1)));
@@ -488,17 +519,18 @@ attn_fwd_tc_kernel(const AttnParams p,
 
       // Rows that already hold a finite running max exponentiate against it straight away
       // (one pass); the max only moves when a score exceeds it by more than the threshold.
-      const bool slow = __any_sync(0xffffffffu, m == -INFINITY);
+      if (!all_finite) all_finite = !__any_sync(0xffffffffu, m == -INFINITY);
+      const bool slow = !all_finite;
       float m_new = m, alpha = 1.f, m_ref = m;
       bool second_pass = true;
       if (!slow) {
         float sum, xmax;
-        if (p.debug & 8) softmax_pass<T, true, true>(tS_half, tP_half, scale, m, w0, w1, sum, xmax);
-        else if (masked) softmax_pass<T, true>(tS_half, tP_half, scale, m, w0, w1, sum, xmax);
-        else        softmax_pass<T, false>(tS_half, tP_half, scale, m, w0, w1, sum, xmax);
+        if (p.debug & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m, w, sum, xmax);
+        else if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
+        else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
         *xch_mine = xmax;
-        ptx::named_bar_sync(1 + lq, 64);
-        const float xrow = fmaxf(xmax, *xch_other);
+        ptx::named_bar_sync(1 + lq, 32 * kSplit);
+        const float xrow = row_max();
         if (!__any_sync(0xffffffffu, xrow > kRescaleThreshold)) {
           l += sum;
           second_pass = false;
@@ -509,37 +541,36 @@ attn_fwd_tc_kernel(const AttnParams p,
         }
       } else {
         float smax;
-        if (masked) max_pass<true>(tS_half, w0, w1, smax);
-        else        max_pass<false>(tS_half, w0, w1, smax);
+        if (masked) max_pass<true, kCW>(tS_mine, w, smax);
+        else        max_pass<false, kCW>(tS_mine, w, smax);
         *xch_mine = smax;
-        ptx::named_bar_sync(1 + lq, 64);
-        const float m_tile = fmaxf(smax, *xch_other) * scale;     // lines 48 / 50
+        ptx::named_bar_sync(1 + lq, 32 * kSplit);
+        const float srow = row_max();
+        const float m_tile = srow * scale;                        // lines 48 / 50
         const float m_cand = fmaxf(m, m_tile);
         if (m == -INFINITY) { m_new = m_cand; }                   // nothing accumulated yet
         else if (m_cand > m + kRescaleThreshold) { m_new = m_cand; alpha = ex2_approx(m - m_new); }
         m_ref = (m_new == -INFINITY) ? 0.f : m_new;               // guard the reference lacks (line 53)
       }
       if (second_pass) {
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this half's columns
-          // O must hold every product up to step j-1 before it is rescaled.  P.V(j-2) is known to be
-          // complete (waited for above), so this barrier is at most one phase behind.
-          ok = ptx::mbar_wait(bar(BAR_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this thread's O columns
+          // O must hold every product up to step j-1 before it is rescaled.  P.V(j-2) completed
+          // before S(j) was issued, so this barrier is at most one phase behind.
+          ptx::mbar_wait(bar(BAR_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
           ptx::tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) {
-            uint32_t r[32];
-            ptx::tmem_ld32(tO_half + c * 32, r);
+          for (int c = 0; c < kOC / kOChunk; ++c) {
+            uint32_t r[kOChunk];
+            tmem_load_cols<kOChunk>(tO_mine + c * kOChunk, r);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            ptx::tmem_st32(tO_half + c * 32, r);
+            for (int i = 0; i < kOChunk; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_store_cols<kOChunk>(tO_mine + c * kOChunk, r);
           }
         }
         float sum, xmax;
-        if (masked) softmax_pass<T, true>(tS_half, tP_half, scale, m_ref, w0, w1, sum, xmax);
-        else        softmax_pass<T, false>(tS_half, tP_half, scale, m_ref, w0, w1, sum, xmax);
+        if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
+        else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
         l = l * alpha + sum;                                      // line 57
         m = m_new;                                                // line 56
       }
@@ -549,32 +580,32 @@ attn_fwd_tc_kernel(const AttnParams p,
       ptx::mbar_arrive(bar(BAR_P_FULL + (j & 1)));
       if (threadIdx.x == 128) SA_TRACE_EVENT(4, 4, j);
     }
-    if (ok) {
-      ok = ptx::mbar_wait(bar(BAR_O_FULL), 0, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
+    ptx::mbar_wait(bar(BAR_O_FULL), 0, abort_flag);
+    // A wait that ran out leaves the abort flag set; nothing is written in that case.
+    float* xch_mine = xch + ((n_steps & 1) * kSplit + quarter) * 128 + row;
+    const float* xch_row = xch + (n_steps & 1) * kSplit * 128 + row;
+    *xch_mine = l;
+    ptx::named_bar_sync(1 + lq, 32 * kSplit);
+    if (*abort_flag == 0) {
       ptx::tc_fence_after();
-      float* xch_mine = xch + ((n_steps & 1) * 2 + half) * 128 + row;
-      const float* xch_other = xch + ((n_steps & 1) * 2 + (half ^ 1)) * 128 + row;
-      *xch_mine = l;
-      ptx::named_bar_sync(1 + lq, 64);
-      const float l_row = l + *xch_other;
-      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;          // line 144, with 0 for an empty row
-      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / 2) * half);
+      float l_row = xch_row[0];
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(tO_half + c * 32, r);
+      for (int g = 1; g < kSplit; ++g) l_row += xch_row[128 * g];
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;          // line 144, with 0 for an empty row
+      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + kOC * quarter);
+#pragma unroll
+      for (int c = 0; c < kOC / kOChunk; ++c) {
+        uint32_t r[kOChunk];
+        tmem_load_cols<kOChunk>(tO_mine + c * kOChunk, r);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kOChunk / 8; ++i) {
           uint4 v;
           v.x = Fmt<T>::pack2(__uint_as_float(r[8 * i + 0]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
           v.y = Fmt<T>::pack2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
           v.z = Fmt<T>::pack2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
           v.w = Fmt<T>::pack2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-          dst[c * 4 + i] = v;                             // line 146
+          dst[c * (kOChunk / 8) + i] = v;                 // line 146
         }
       }
     }

@@ -158,6 +158,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -207,8 +216,29 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
 }
 __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
+}
+// 2^x for a pair of fp32 values on the FMA pipe (no MUFU): round-to-nearest range reduction by
+// a magic-number add, a cubic for 2^f on [-0.5, 0.5] (relative error below 8e-5) and an integer
+// add into the exponent field.  x is clamped to >= -126, where the result is a denormal that
+// flush-to-zero arithmetic reads as 0; x must stay below 127 (callers re-do the pass long before:
+// any x above the rescale threshold forces one).
+__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& p0, float& p1) {
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  const uint64_t x2 = pack_f32x2(x0, x1);
+  const uint64_t t2 = add_f32x2(x2, pack_f32x2(12582912.f, 12582912.f));
+  const uint64_t xi2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f32x2(xi2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t r2 = fma_f32x2(pack_f32x2(0.05508868f, 0.05508868f), f2, pack_f32x2(0.24260405f, 0.24260405f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.69327623f, 0.69327623f));
+  r2 = fma_f32x2(r2, f2, pack_f32x2(0.99992895f, 0.99992895f));
+  float r0, r1, t0, t1;
+  unpack_f32x2(r2, r0, r1);
+  unpack_f32x2(t2, t0, t1);
+  p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
