@@ -8,10 +8,11 @@
 //   cells kernel   one warp per 32-row x 512-column strip: each lane streams 32 rows of
 //                  16 bytes, reduces them to "any / all" flags of the 32x32 cells (a lane
 //                  pair per cell) and, optionally, emits the packed bit-plane stage 2 reads.
-//   lists kernel   one warp per (mask plane, query block): folds the cell flags of each
-//                  BLOCK_Q x BLOCK_K tile, ballots the full / partial predicates over 32
-//                  tiles at a time and writes the ascending id lists by a popcount
-//                  prefix (order of mask_utils.py:66-79), tails filled with -1.
+//   lists kernel   one CTA per (mask plane, query block), launched as a programmatic
+//                  dependent of the cells kernel: folds the cell flags of each
+//                  BLOCK_Q x BLOCK_K tile, ballots the full / partial predicates and writes the
+//                  ascending id lists by a popcount prefix (order of mask_utils.py:66-79),
+//                  tails filled with -1.
 #include "sa_common.cuh"
 
 namespace sa {
@@ -39,6 +40,8 @@ constexpr int kCellsThreads = 256;
 
 __global__ void __launch_bounds__(kCellsThreads)
 classify_cells_kernel(const ClassifyParams p, const int chunks_per_row, const long long n_strips) {
+  // lets the lists kernel be scheduled early; it waits for this grid to complete before reading
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const long long warp0 = (static_cast<long long>(blockIdx.x) * kCellsThreads + threadIdx.x) >> 5;
   const long long n_warps = (static_cast<long long>(gridDim.x) * kCellsThreads) >> 5;
@@ -101,10 +104,15 @@ classify_cells_kernel(const ClassifyParams p, const int chunks_per_row, const lo
 
 constexpr int kListsThreads = 128;
 
+// One CTA per (mask plane, query block): 128 tiles per pass, one per thread; the order of the ids
+// (ascending kv block, mask_utils.py:66-79) comes from a ballot within each warp and a prefix over
+// the four warps.
 __global__ void __launch_bounds__(kListsThreads)
 compact_lists_kernel(const ClassifyParams p, const int n_rows) {
-  const int lane = threadIdx.x & 31;
-  const int row = (blockIdx.x * kListsThreads + threadIdx.x) >> 5;   // (plane, query block)
+  asm volatile("griddepcontrol.wait;" ::: "memory");     // the cell flags of the streaming kernel are complete
+  __shared__ int s_full[kListsThreads / 32], s_part[kListsThreads / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x;                                       // (plane, query block)
   if (row >= n_rows) return;
   const int nq = p.Sq / p.BQ, nk = p.Sk / p.BK;
   const int rq = p.BQ / kCell, rk = p.BK / kCell;
@@ -115,8 +123,8 @@ compact_lists_kernel(const ClassifyParams p, const int n_rows) {
   int32_t* p_out = p.part_ids + static_cast<int64_t>(row) * nk;
   const uint32_t lt_mask = (1u << lane) - 1u;
   int nf = 0, np = 0;
-  for (int j0 = 0; j0 < nk; j0 += 32) {
-    const int j = j0 + lane;
+  for (int j0 = 0; j0 < nk; j0 += kListsThreads) {
+    const int j = j0 + tid;
     uint32_t any = 0u, all = 2u;
     if (j < nk) {
       for (int y = 0; y < rq; ++y) {
@@ -132,14 +140,24 @@ compact_lists_kernel(const ClassifyParams p, const int n_rows) {
     const bool is_part = (j < nk) && !is_full && (any & 1u);     // 0 < count       (mask_utils.py:76)
     const uint32_t bf = __ballot_sync(0xffffffffu, is_full);
     const uint32_t bp = __ballot_sync(0xffffffffu, is_part);
-    if (is_full) f_out[nf + __popc(bf & lt_mask)] = j;
-    if (is_part) p_out[np + __popc(bp & lt_mask)] = j;
-    nf += __popc(bf);
-    np += __popc(bp);
+    if (lane == 0) { s_full[warp] = __popc(bf); s_part[warp] = __popc(bp); }
+    __syncthreads();
+    int off_f = nf, off_p = np, tot_f = 0, tot_p = 0;
+#pragma unroll
+    for (int w = 0; w < kListsThreads / 32; ++w) {
+      if (w < warp) { off_f += s_full[w]; off_p += s_part[w]; }
+      tot_f += s_full[w];
+      tot_p += s_part[w];
+    }
+    if (is_full) f_out[off_f + __popc(bf & lt_mask)] = j;
+    if (is_part) p_out[off_p + __popc(bp & lt_mask)] = j;
+    nf += tot_f;
+    np += tot_p;
+    __syncthreads();
   }
-  for (int t = nf + lane; t < nk; t += 32) f_out[t] = -1;
-  for (int t = np + lane; t < nk; t += 32) p_out[t] = -1;
-  if (lane == 0) {
+  for (int t = nf + tid; t < nk; t += kListsThreads) f_out[t] = -1;
+  for (int t = np + tid; t < nk; t += kListsThreads) p_out[t] = -1;
+  if (tid == 0) {
     p.full_lens[row] = nf;                                       // mask_utils.py:81
     p.part_lens[row] = np;                                       // mask_utils.py:82
   }
@@ -173,9 +191,17 @@ cudaError_t launch_classify(const ClassifyParams& p, cudaStream_t stream) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int n_rows = planes * (p.Sq / p.BQ);
-  const int ctas2 = (n_rows * 32 + kListsThreads - 1) / kListsThreads;
-  compact_lists_kernel<<<ctas2, kListsThreads, 0, stream>>>(p, n_rows);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(n_rows));
+  cfg.blockDim = dim3(kListsThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, compact_lists_kernel, p, n_rows);
 }
 
 }  // namespace sa
