@@ -112,6 +112,13 @@ template <> struct Fmt<__nv_bfloat16> {
 
 // Developer tracing (compiled out unless SA_TRACE is defined): CTA (0,0) appends
 // (event, step, SM clock) triples per role to a device array read back by sa_debug_read_trace().
+// Developer experiments (switching stages of the pipeline off) exist only in tracing builds.
+#ifdef SA_TRACE
+#define SA_DEBUG_FLAGS (p.debug)
+#else
+#define SA_DEBUG_FLAGS 0
+#endif
+
 #ifdef SA_TRACE
 constexpr int kTraceCap = 500;                  // events per role, kept in shared memory
 __device__ long long g_trace[5 * 4096];
@@ -344,12 +351,12 @@ attn_fwd_tc_kernel(const AttnParams p,
       const uint32_t full_bar = bar(bar_full + st);
       if (lane == 0) {
         if (round > 0) ok = ptx::mbar_wait(bar(bar_empty + st), (round - 1) & 1, abort_flag);
-        if (ok) ptx::mbar_arrive_expect_tx(full_bar, (p.debug & 2) ? slot_bytes : L::kTileBytes);
+        if (ok) ptx::mbar_arrive_expect_tx(full_bar, (SA_DEBUG_FLAGS & 2) ? slot_bytes : L::kTileBytes);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (lane == 0) SA_TRACE_EVENT(warp, 1, j);
       const int id_c = __shfl_sync(0xffffffffu, id_cur, c_of_lane & 3);
-      if (ok && c_of_lane < eps && (!(p.debug & 2) || lane == 0))
+      if (ok && c_of_lane < eps && (!(SA_DEBUG_FLAGS & 2) || lane == 0))
         ptx::tma_load_4d(dst + pnl_of_lane * kPanelBytes + c_of_lane * slot_bytes, tm, full_bar,
                          pnl_of_lane * 64, id_c * p.BK, ch, cb);
       if (lane == 0) SA_TRACE_EVENT(warp, 2, j);
@@ -411,7 +418,7 @@ attn_fwd_tc_kernel(const AttnParams p,
         for (int kk = 0; kk < D / 16; ++kk) {
           constexpr uint32_t kPanelStep = kPanelBytes >> 4;
           const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
-          if ((p.debug & 4) && kk > 0) break;
+          if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
           if (kk == 0) ptx::mma_ss_lo<false>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
           else         ptx::mma_ss_lo<true>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
         }
@@ -444,14 +451,14 @@ attn_fwd_tc_kernel(const AttnParams p,
         if (j == 0) {
 #pragma unroll
           for (int kk = 0; kk < kTileN / 16; ++kk) {
-            if ((p.debug & 4) && kk > 0) break;
+            if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
             if (kk == 0) ptx::mma_ts_lo<false>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
             else         ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
           }
         } else {
 #pragma unroll
           for (int kk = 0; kk < kTileN / 16; ++kk) {
-            if ((p.debug & 4) && kk > 0) break;
+            if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
             ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
           }
         }
@@ -510,7 +517,7 @@ attn_fwd_tc_kernel(const AttnParams p,
         for (int g = 1; g < kSplit; ++g) v = fmaxf(v, xch_row[128 * g]);
         return v;
       };
-      if (p.debug & 1) {
+      if (SA_DEBUG_FLAGS & 1) {
         ptx::tc_fence_before();
         ptx::mbar_arrive(bar(BAR_P_FULL + (j & 1)));
         continue;
@@ -525,7 +532,7 @@ attn_fwd_tc_kernel(const AttnParams p,
       bool second_pass = true;
       if (!slow) {
         float sum, xmax;
-        if (p.debug & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m, w, sum, xmax);
+        if (SA_DEBUG_FLAGS & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m, w, sum, xmax);
         else if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
         else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
         *xch_mine = xmax;

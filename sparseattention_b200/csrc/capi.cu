@@ -144,7 +144,9 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   p.part_lens = part_lens; copy_n(p.pls, part_lens_strides, 3);
   p.scale_log2 = scale_log2;
   p.dev_status = dev_status;
+#ifdef SA_TRACE
   { const char* e = getenv("SA_TC_DEBUG"); p.debug = e ? atoi(e) : 0; }
+#endif
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   const bool tc_ok = sa::attn_tc_supported(p) != 0;
