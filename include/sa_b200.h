@@ -78,6 +78,23 @@ int sa_classify_mask(const uint8_t* mask,
                      void* workspace, size_t workspace_bytes,
                      void* stream);
 
+/* No counterpart in the reference.  The same classification as sa_classify_mask() for hosts that
+ * cannot hand over a workspace because they cannot allocate device memory where this is called
+ * (memory fully committed at start-up, allocator off-limits inside a foreign runtime's callback,
+ * latency budget with no room for an allocation).  The scratch is a fixed device array inside the
+ * library, SA_STATIC_SCRATCH_BYTES long, resident on every GPU that loads the library; the call
+ * allocates nothing.  Masks whose scratch need (sa_classify_workspace_bytes) exceeds it are refused
+ * with SA_ERR_WORKSPACE.  The first call on a device looks the array's address up (set-up work: make
+ * that call before starting any stream capture).  All calls share the array, so calls that may
+ * overlap on the GPU must be serialised by the caller. */
+#define SA_STATIC_SCRATCH_BYTES (1u << 20)
+int sa_classify_mask_static(const uint8_t* mask,
+                            int64_t stride_b, int64_t stride_h, int64_t stride_q, int64_t stride_k,
+                            int B, int H, int Sq, int Sk, int BLOCK_Q, int BLOCK_K,
+                            int32_t* full_ids, int32_t* full_lens,
+                            int32_t* part_ids, int32_t* part_lens,
+                            uint32_t* packed_bits, void* stream);
+
 /* Whether SA_IMPL_AUTO would pick the tcgen05 kernel for this call (1) or the SIMT kernel (0). */
 int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int Sk,
                          const void* q, const void* k, const void* v,

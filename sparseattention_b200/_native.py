@@ -35,6 +35,7 @@ SYMBOLS = {
     "sa_unique_planes": (_i, [_i, _i, _i64, _i64, _pi, _pi]),
     "sa_classify_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "sa_classify_mask": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "sa_classify_mask_static": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "sa_attn_uses_tcgen05": (_i, [_i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i]),
     "sa_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p,
                          _i, _i, _i, _i, _i, _i, _i, _i,

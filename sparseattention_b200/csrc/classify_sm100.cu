@@ -205,3 +205,51 @@ cudaError_t launch_classify(const ClassifyParams& p, cudaStream_t stream) {
 }
 
 }  // namespace sa
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the classifier entry point.
+//
+// sa_classify_mask() needs a caller-provided workspace for the cell flags that travel between its
+// two kernels.  Some hosts have no way to provide one: a serving process whose device memory was
+// carved up once at start-up and is fully committed (KV caches, weights), a plugin that runs inside
+// another runtime's callback where calling the allocator is not permitted, a hard-latency loop in
+// which an allocation (and the implicit synchronisation a cudaMalloc / cudaFree can bring) is not
+// affordable.  For them the flags live in the fixed device array below: SA_STATIC_SCRATCH_BYTES
+// bytes that every GPU which loads this library holds until the process exits.
+//
+// The array's name is only a host-side handle; the device address is looked up once per device
+// with cudaGetSymbolAddress (with that device current) on the first call made on it.  That first
+// call therefore does set-up work and should be made before any stream capture is started.
+// Every call uses the same array: it keeps the flags of the previous call (every flag a call reads
+// is written by that call first, so nothing needs clearing), and two calls whose kernels overlap on
+// the GPU - different streams, or different host threads - race on it.  Serialise them.
+static __device__ __align__(256) uint8_t g_static_scratch[SA_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+uint8_t* g_static_scratch_addr[kMaxDevices] = {};
+}  // namespace
+
+extern "C" int sa_classify_mask_static(const uint8_t* mask,
+                                       int64_t stride_b, int64_t stride_h, int64_t stride_q, int64_t stride_k,
+                                       int B, int H, int Sq, int Sk, int BLOCK_Q, int BLOCK_K,
+                                       int32_t* full_ids, int32_t* full_lens,
+                                       int32_t* part_ids, int32_t* part_lens,
+                                       uint32_t* packed_bits, void* stream) {
+  if (B <= 0 || H <= 0 || Sq <= 0 || Sk <= 0) return SA_ERR_INVALID_ARGUMENT;
+  int Bu = 1, Hu = 1;
+  if (sa_unique_planes(B, H, stride_b, stride_h, &Bu, &Hu) != SA_OK) return SA_ERR_INVALID_ARGUMENT;
+  const size_t need = sa_classify_workspace_bytes(Bu, Hu, Sq, Sk);
+  if (need == 0) return SA_ERR_INVALID_ARGUMENT;
+  if (need > SA_STATIC_SCRATCH_BYTES) return SA_ERR_WORKSPACE;    // mask too large for the fixed array
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SA_ERR_NO_DEVICE;
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_static_scratch) != cudaSuccess || addr == nullptr) return SA_ERR_CUDA;
+    g_static_scratch_addr[dev] = static_cast<uint8_t*>(addr);
+  }
+  return sa_classify_mask(mask, stride_b, stride_h, stride_q, stride_k, B, H, Sq, Sk, BLOCK_Q, BLOCK_K,
+                          full_ids, full_lens, part_ids, part_lens, packed_bits,
+                          g_static_scratch_addr[dev], SA_STATIC_SCRATCH_BYTES, stream);
+}
