@@ -359,6 +359,15 @@ def run_ours(args):
         torch.distributed.destroy_process_group()
 
 
+def _quiet_stdout():
+    """Libraries (NCCL's version banner) write to the process's stdout; the one JSON line must be
+    the only thing there.  Returns a file object bound to the real stdout and points fd 1 at stderr."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -372,10 +381,13 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="profiling: override the batch size of the workload")
     ap.add_argument("--ps", default="", help="profiling: comma-separated subset of the drop probabilities")
     args = ap.parse_args()
+    out = _quiet_stdout()
+    sys.stdout = out
     if args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
+    out.flush()
 
 
 if __name__ == "__main__":
