@@ -3,26 +3,29 @@
 // Replaces sparseattention/sparse_attn_kernel.py:72-146 (kernel) and 10-63 (inner loop)
 // for fp16 / bf16, head dim 64 or 128, BLOCK_Q = 128 and BLOCK_K in {32, 64, 128}.
 //
-// One CTA (one per SM, 320 threads) owns one query block (128 rows) of one (batch, head) and
+// One CTA (one per SM, 384 threads) owns one query block (128 rows) of one (batch, head) and
 // walks its two kv-block lists -- the full list first, then the partial list: the order of
 // sparse_attn_kernel.py:113-142 -- in steps of 128 kv rows (128 / BLOCK_K listed blocks):
 //
-//   warp 0    producer.  Reads the lists and, in the order the tensor core will consume them,
-//             gathers the listed kv blocks of K and of V into 128-row, 128-byte-swizzled tiles
-//             of a five-stage shared-memory ring with TMA tile loads whose row coordinate comes
-//             from the list, plus the 512-byte bit-mask tiles of the partial blocks
-//             (cp.async.bulk from the packed plane of stage 1).
-//   warp 1    MMA issuer.  S(j) = Q.K(j)^T into one of two score buffers in tensor memory
-//             (tcgen05.mma, operands in shared memory), always one step ahead of the softmax;
-//             O += P(j).V(j) with P read from tensor memory.
-//   warps 2-9 softmax; a thread owns a query row and one half of the 128 score columns.  Scores
-//             are exponentiated against the row's running max in a single pass (base 2, scale
-//             folded as in sparse_attn_kernel.py:152); the max moves, and O is rescaled in
-//             tensor memory, only when a score exceeds it by more than 2^8.  Steps that contain
-//             a partial or padding block apply the bit mask; steps of full blocks do no mask
-//             work.  P (rounded to the V dtype, line 61) overwrites the head of the thread's own
-//             score columns; row sums stay in fp32 (line 57).  Finally O / l is written; a row
-//             with no attended key yields 0 (the reference yields NaN, line 53).
+//   warp 0     K producer.  Reads the lists and gathers the listed kv blocks of K into 128-row,
+//              128-byte-swizzled tiles of a three-stage shared-memory ring with TMA tile loads whose
+//              row coordinate comes from the list (eight lanes issue the eight boxes of a tile),
+//              plus the 512-byte bit-mask tiles of the partial blocks (cp.async.bulk from the
+//              packed plane of stage 1, four-stage ring).
+//   warp 1     V producer: the same for V, two-stage ring.
+//   warp 2     S issuer.  S(j) = Q.K(j)^T into one of two score buffers in tensor memory
+//              (tcgen05.mma, both operands in shared memory), one step ahead of the softmax.
+//   warp 3     P.V issuer.  O += P(j).V(j) with P read from its own buffer in tensor memory.
+//   warps 4-11 softmax; a thread owns a query row and one half of the 128 score columns.  Scores
+//              are exponentiated against the row's running max in a single pass (base 2, scale
+//              folded as in sparse_attn_kernel.py:152); the max moves, and O is rescaled in
+//              tensor memory, only when a score exceeds it by more than 2^8 (the pass is then
+//              redone from the intact scores).  Steps that contain a partial or padding block apply
+//              the bit mask; steps of full blocks do no mask work.  P is rounded to the V dtype
+//              (line 61); row sums stay in fp32 (line 57).  Finally O / l is written; a row with no
+//              attended key yields 0 (the reference yields NaN, line 53).
+//
+// Tensor memory (512 columns): score buffers at 0 and 128, O at 256, P buffers at 384 and 448.
 //
 // A step whose last slots run past the end of the lists re-loads the first listed block with an
 // all-zero mask word.  Every mbarrier wait is bounded; on expiry the CTA reports
