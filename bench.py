@@ -336,7 +336,8 @@ def run_ours(args):
                        "flop_accounting": "4*D*BQ*BK per listed (non-skipped) tile, both stages timed",
                        "shard": "each rank owns a full (batch, head) shard of the workload"},
             "roofline": {"bound": "tensor", "achieved": att_tflops, "peak": peaks["bf16_tflops_sustained"],
-                         "unit": "TFLOP/s", "frac": att_tflops / peaks["bf16_tflops_sustained"], "traffic": None,
+                         "unit": "TFLOP/s", "frac": att_tflops / peaks["bf16_tflops_sustained"],
+                         "traffic": 254.65e6 * B / 2.0, "traffic_unit": "bytes per launch (ncu capture at B=2, p=0.5, scaled by batch)",
                          "kernel": "attn_fwd_tc_kernel<bf16,128>", "peak_source": peak_kind + " (sustained bf16 matmul)",
                          "note": "FLOPs of the listed tiles of all six launches / sum of their durations (CUDA events)"},
             "roofline_classifier": {"bound": "hbm", "achieved": cls_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
