@@ -3,12 +3,14 @@
 // Replaces sparseattention/sparse_attn_kernel.py:72-146 (kernel) and 10-63 (inner loop)
 // for fp16 / bf16, head dim 64 or 128, BLOCK_Q = 128 and BLOCK_K in {32, 64, 128}.
 //
-// One CTA (one per SM, 384 threads) owns one query block (128 rows) of one (batch, head) and
-// walks its two kv-block lists -- the full list first, then the partial list: the order of
+// Persistent grid: one CTA per SM (384 threads) walks the (query block, batch, head) tiles
+// blockIdx.x, blockIdx.x + gridDim.x, ...; the loads and first MMAs of a tile overlap the epilogue
+// of the previous one (Q is double-buffered, barrier phases run on across tiles).  For a tile --
+// one query block (128 rows) of one (batch, head) -- the CTA walks its two kv-block lists -- the full list first, then the partial list: the order of
 // sparse_attn_kernel.py:113-142 -- in steps of 128 kv rows (128 / BLOCK_K listed blocks):
 //
 //   warp 0     K producer.  Reads the lists and gathers the listed kv blocks of K into 128-row,
-//              128-byte-swizzled tiles of a three-stage shared-memory ring with TMA tile loads whose
+//              128-byte-swizzled tiles of a two-stage shared-memory ring with TMA tile loads whose
 //              row coordinate comes from the list (eight lanes issue the eight boxes of a tile),
 //              plus the 512-byte bit-mask tiles of the partial blocks (cp.async.bulk from the
 //              packed plane of stage 1, four-stage ring).
@@ -49,7 +51,7 @@ constexpr int kSplit = SA_SOFTMAX_SPLIT;      // threads per query row in the so
 constexpr int kThreadsTC = 128 + 128 * kSplit;   // warps: K producer, V producer, S issuer, P.V issuer, 4 * kSplit softmax
 constexpr int kSoftmaxWarp0 = 4;     // first softmax warp (a multiple of 4: TMEM lane quarter = warp % 4)
 constexpr uint32_t kTmemCols = 512;  // score buffers at columns 0 and 128, O at 256, P buffers at 384 and 448
-constexpr int kStagesK = 3;          // K tiles in flight in shared memory
+constexpr int kStagesK = 2;          // K tiles in flight in shared memory
 constexpr int kStagesV = 2;          // V tiles in flight in shared memory
 constexpr int kBitStages = 4;        // steps of bit-mask tiles in flight
 constexpr uint32_t kPanelBytes = 128u * 128u;   // 128 rows x 64 elements x 2 B
@@ -64,15 +66,17 @@ constexpr float kRescaleThreshold = 8.0f;       // log2 units
 constexpr int kPolyPlain = SA_POLY_PLAIN, kPolyMasked = SA_POLY_MASKED;
 
 enum Bar : int {
-  BAR_Q = 0,
-  BAR_K_FULL,                                      // kStagesK: K tile landed
+  BAR_Q_FULL = 0,                                  // 2: Q tile of a query block landed
+  BAR_Q_EMPTY = BAR_Q_FULL + 2,                    // 2: last S of the tile that used the Q slot complete
+  BAR_K_FULL = BAR_Q_EMPTY + 2,                                      // kStagesK: K tile landed
   BAR_K_EMPTY = BAR_K_FULL + kStagesK,             // kStagesK: K tile consumed by S = Q.K^T
   BAR_V_FULL = BAR_K_EMPTY + kStagesK,             // kStagesV
   BAR_V_EMPTY = BAR_V_FULL + kStagesV,             // kStagesV: V tile consumed by O += P.V
   BAR_S_FULL = BAR_V_EMPTY + kStagesV,             // 2: scores of buffer j & 1 complete
   BAR_P_FULL = BAR_S_FULL + 2,                     // 2: P of buffer j & 1 written (and S read) by all softmax threads
   BAR_PV_DONE = BAR_P_FULL + 2,                    // 2: O += P.V of step j complete (barrier j & 1)
-  BAR_O_FULL = BAR_PV_DONE + 2,                    // last O += P.V complete
+  BAR_O_FULL = BAR_PV_DONE + 2,                    // last O += P.V of a tile complete
+  BAR_O_FREE,                                      // the epilogue has read O out of tensor memory
   BAR_BITS_FULL,                                   // kBitStages
   BAR_BITS_EMPTY = BAR_BITS_FULL + kBitStages,
   BAR_COUNT = BAR_BITS_EMPTY + kBitStages
@@ -82,13 +86,13 @@ template <int D>
 struct Smem {
   static constexpr uint32_t kTileBytes = kPanelBytes * (D / 64);
   static constexpr uint32_t off_q = 0;
-  static constexpr uint32_t off_k = kTileBytes;
+  static constexpr uint32_t off_k = 2 * kTileBytes;              // two Q tiles first
   static constexpr uint32_t off_v = off_k + kStagesK * kTileBytes;
   static constexpr uint32_t off_bits = off_v + kStagesV * kTileBytes;      // [kBitStages][4 sub-slots][128 rows] u32
   static constexpr uint32_t off_bar = off_bits + kBitStages * 4 * 128 * 4;
   static constexpr uint32_t off_misc = off_bar + 8 * 32;
-  static constexpr uint32_t off_xch = off_misc + 16;             // [2 parities][kSplit column groups][128 rows] f32
-  static constexpr uint32_t total = off_xch + 2 * kSplit * 128 * 4;
+  static constexpr uint32_t off_xch = off_misc + 16;             // [2 parities + epilogue][kSplit column groups][128 rows] f32
+  static constexpr uint32_t total = off_xch + 3 * kSplit * 128 * 4;
 #ifdef SA_TRACE
   static constexpr uint32_t dynamic_bytes = total + 1024 + 5 * 500 * 8;
 #else
@@ -220,12 +224,35 @@ __device__ __forceinline__ void tmem_store_cols(uint32_t taddr, const uint32_t (
   if constexpr (kCols == 32) ptx::tmem_st32(taddr, r); else ptx::tmem_st16(taddr, r);
 }
 
+// Work of one (query block, batch, head) tile, read from the lists.
+struct TileInfo {
+  int b, h, qblk;
+  int n_full, n_part, total, n_steps, n_plain;
+};
+
+__device__ __forceinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq, int nk, int eps) {
+  TileInfo t;
+  const int bh = tile / nq;
+  t.qblk = tile % nq;
+  t.b = bh / p.H;
+  t.h = bh % p.H;
+  int n_full = p.full_lens[t.b * p.fls[0] + t.h * p.fls[1] + static_cast<int64_t>(t.qblk) * p.fls[2]];  // line 107
+  int n_part = p.part_lens[t.b * p.pls[0] + t.h * p.pls[1] + static_cast<int64_t>(t.qblk) * p.pls[2]];  // line 127
+  t.n_full = min(max(n_full, 0), nk);
+  t.n_part = min(max(n_part, 0), nk);
+  t.total = t.n_full + t.n_part;
+  t.n_steps = (t.total + eps - 1) / eps;
+  t.n_plain = t.n_full / eps;          // leading steps made of full blocks only
+  return t;
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreadsTC, 1)
 attn_fwd_tc_kernel(const AttnParams p,
                    const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v) {
+                   const __grid_constant__ CUtensorMap tm_v,
+                   const int n_tiles) {
   using L = Smem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -240,39 +267,24 @@ attn_fwd_tc_kernel(const AttnParams p,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef SA_TRACE
-  const bool trace_on = blockIdx.x == 16 && blockIdx.y == 40;
+  const bool trace_on = blockIdx.x == 16;
   int trace_n[5] = {0, 0, 0, 0, 0};
   long long* trace_buf = reinterpret_cast<long long*>(smem + L::total);
   if (trace_on) for (int i = threadIdx.x; i < 5 * kTraceCap; i += blockDim.x) trace_buf[i] = 0;
 #endif
-  const int qblk = blockIdx.x;
-  const int b = blockIdx.y / p.H, h = blockIdx.y % p.H;
+  const int nq = p.Sq / kTileM;
   const int nk = p.Sk / p.BK;
   const int eps = kTileN / p.BK;        // list entries per step
   const int sps = p.BK / 32;            // 32-column sub-slots per entry
 
-  int n_full = p.full_lens[b * p.fls[0] + h * p.fls[1] + static_cast<int64_t>(qblk) * p.fls[2]];  // line 107
-  int n_part = p.part_lens[b * p.pls[0] + h * p.pls[1] + static_cast<int64_t>(qblk) * p.pls[2]];  // line 127
-  n_full = min(max(n_full, 0), nk);
-  n_part = min(max(n_part, 0), nk);
-  const int total = n_full + n_part;
-  const int n_steps = (total + eps - 1) / eps;
-  const int n_plain = n_full / eps;     // leading steps made of full blocks only
-
-  T* o_base = static_cast<T*>(p.o) + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(qblk) * kTileM * p.os[2];
-
-  if (total == 0) {                     // nothing attended: rows are 0, no tensor memory needed
-    if (warp >= kSoftmaxWarp0) {
-      const int row = (warp & 3) * 32 + lane;
-      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + (D / kSplit) * ((warp - kSoftmaxWarp0) >> 2));
-#pragma unroll
-      for (int i = 0; i < D / (8 * kSplit); ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    return;
-  }
-
   if (threadIdx.x == 0) {
-    ptx::mbar_init(bar(BAR_Q), 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(bar(BAR_Q_FULL + i), 1);
+      ptx::mbar_init(bar(BAR_Q_EMPTY + i), 1);
+      ptx::mbar_init(bar(BAR_S_FULL + i), 1);
+      ptx::mbar_init(bar(BAR_P_FULL + i), 128 * kSplit);
+      ptx::mbar_init(bar(BAR_PV_DONE + i), 1);
+    }
     for (int i = 0; i < kStagesK; ++i) {
       ptx::mbar_init(bar(BAR_K_FULL + i), 1);
       ptx::mbar_init(bar(BAR_K_EMPTY + i), 1);
@@ -281,12 +293,8 @@ attn_fwd_tc_kernel(const AttnParams p,
       ptx::mbar_init(bar(BAR_V_FULL + i), 1);
       ptx::mbar_init(bar(BAR_V_EMPTY + i), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(bar(BAR_S_FULL + i), 1);
-      ptx::mbar_init(bar(BAR_P_FULL + i), 128 * kSplit);
-      ptx::mbar_init(bar(BAR_PV_DONE + i), 1);
-    }
     ptx::mbar_init(bar(BAR_O_FULL), 1);
+    ptx::mbar_init(bar(BAR_O_FREE), 128 * kSplit);
     for (int i = 0; i < kBitStages; ++i) {
       ptx::mbar_init(bar(BAR_BITS_FULL + i), 1);
       ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 128 * kSplit);
@@ -305,171 +313,210 @@ attn_fwd_tc_kernel(const AttnParams p,
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tO = tmem_base + 256;   // score buffer s lives at tmem_base + 128 * s, P buffer s at 384 + 64 * s
 
+  // Every role walks the same sequence of tiles (blockIdx.x, + gridDim.x, ...) and keeps the same
+  // running counts -- steps done (g), masked steps done (gu), non-empty tiles done (tq) -- from which
+  // buffer indices and barrier phases follow; nothing is reset between tiles, so the loads and the
+  // first MMAs of a tile overlap the epilogue of the previous one.
   if (warp < 2) {
     // ------------------------------------------------------------------ producers
-    // Warp 0 gathers the K tiles (and the bit-mask tiles), warp 1 the V tiles.  The whole warp
+    // Warp 0 gathers Q, the K tiles and the bit-mask tiles, warp 1 the V tiles.  The whole warp
     // runs the loop: lane 0 waits for a free stage and arms its barrier, lanes 0-7 each issue one
     // TMA box, lanes 0-3 fetch the list entries of a step.
     const bool is_k = warp == 0;
     const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
     if (lane == 0) {
       ptx::prefetch_tensormap(tm);
-      if (is_k) {
-        ptx::prefetch_tensormap(&tm_q);
-        const int qb = p.qs[0] ? b : 0, qh = p.qs[1] ? h : 0;
-        ptx::mbar_arrive_expect_tx(bar(BAR_Q), L::kTileBytes);
-#pragma unroll
-        for (int pnl = 0; pnl < D / 64; ++pnl)
-          ptx::tma_load_4d(sQ + pnl * kPanelBytes, &tm_q, bar(BAR_Q), pnl * 64, qblk * kTileM, qh, qb);
-      }
+      if (is_k) ptx::prefetch_tensormap(&tm_q);
     }
-    const int cb = is_k ? (p.ks[0] ? b : 0) : (p.vs[0] ? b : 0);
-    const int ch = is_k ? (p.ks[1] ? h : 0) : (p.vs[1] ? h : 0);
     const int n_stages = is_k ? kStagesK : kStagesV;
     const uint32_t s_tiles = is_k ? sK : sV;
     const int bar_full = is_k ? BAR_K_FULL : BAR_V_FULL, bar_empty = is_k ? BAR_K_EMPTY : BAR_V_EMPTY;
-    const int32_t* fids = p.full_ids + b * p.fis[0] + h * p.fis[1] + static_cast<int64_t>(qblk) * p.fis[2];
-    const int32_t* pids = p.part_ids + b * p.pis[0] + h * p.pis[1] + static_cast<int64_t>(qblk) * p.pis[2];
-    const uint32_t* bits_plane = p.bits + b * p.bits_sb + h * p.bits_sh;
-    bool bad_index = false;
-    // kv-block id of entry `lane` of step j (lanes >= entries per step hold 0)
-    auto my_id_of = [&](int j) -> int {
-      if (lane >= eps || j >= n_steps) return 0;
-      const int e = j * eps + lane;
-      const int ee = e < total ? e : 0;           // slots past the end re-load the first listed block
-      int id = ee < n_full ? fids[ee * p.fis[3]] : pids[(ee - n_full) * p.pis[3]];   // line 33
-      if (static_cast<unsigned>(id) >= static_cast<unsigned>(nk)) { bad_index = true; id = 0; }
-      return id;
-    };
     const uint32_t slot_bytes = static_cast<uint32_t>(p.BK) * 128u;
     constexpr int kPanels = D / 64;
     const int c_of_lane = lane / kPanels, pnl_of_lane = lane % kPanels;
+    bool bad_index = false;
     bool ok = true;
-    int id_cur = my_id_of(0), id_nxt = my_id_of(1);
-    int st = 0, round = 0;
-    for (int j = 0; j < n_steps && ok; ++j) {
-      const int id_nxt2 = my_id_of(j + 2);            // fetched two steps before it is needed
-      if (lane == 0) SA_TRACE_EVENT(warp, 0, j);
-      const uint32_t dst = s_tiles + st * L::kTileBytes;
-      const uint32_t full_bar = bar(bar_full + st);
-      if (lane == 0) {
-        if (round > 0) ok = ptx::mbar_wait(bar(bar_empty + st), (round - 1) & 1, abort_flag);
-        if (ok) ptx::mbar_arrive_expect_tx(full_bar, (SA_DEBUG_FLAGS & 2) ? slot_bytes : L::kTileBytes);
-      }
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (lane == 0) SA_TRACE_EVENT(warp, 1, j);
-      const int id_c = __shfl_sync(0xffffffffu, id_cur, c_of_lane & 3);
-      if (ok && c_of_lane < eps && (!(SA_DEBUG_FLAGS & 2) || lane == 0))
-        ptx::tma_load_4d(dst + pnl_of_lane * kPanelBytes + c_of_lane * slot_bytes, tm, full_bar,
-                         pnl_of_lane * 64, id_c * p.BK, ch, cb);
-      if (lane == 0) SA_TRACE_EVENT(warp, 2, j);
-      if (is_k && j >= n_plain && ok) {               // bit-mask tiles of the partial blocks of step j
-        const int u = j - n_plain, bst = u % kBitStages;
-        int n_tiles = 0;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int e = j * eps + c / sps;
-          n_tiles += (e >= n_full && e < total) ? 1 : 0;
-        }
+    int st = 0, round = 0, gu = 0, tq = 0;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+      if (ti.total == 0) continue;
+      const int b = ti.b, h = ti.h, qblk = ti.qblk, n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps,
+                n_plain = ti.n_plain;
+      if (is_k) {                                   // Q tile of this query block, double-buffered
+        const int qs = tq & 1;
         if (lane == 0) {
-          if (u >= kBitStages) ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
+          if (tq >= 2) ok = ptx::mbar_wait(bar(BAR_Q_EMPTY + qs), ((tq >> 1) - 1) & 1, abort_flag);
           if (ok) {
-            if (n_tiles > 0) ptx::mbar_arrive_expect_tx(bar(BAR_BITS_FULL + bst), 512u * n_tiles);
-            else ptx::mbar_arrive(bar(BAR_BITS_FULL + bst));
+            const int qb = p.qs[0] ? b : 0, qh = p.qs[1] ? h : 0;
+            ptx::mbar_arrive_expect_tx(bar(BAR_Q_FULL + qs), L::kTileBytes);
+#pragma unroll
+            for (int pnl = 0; pnl < D / 64; ++pnl)
+              ptx::tma_load_4d(sQ + qs * L::kTileBytes + pnl * kPanelBytes, &tm_q, bar(BAR_Q_FULL + qs),
+                               pnl * 64, qblk * kTileM, qh, qb);
           }
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        const int c = lane & 3, ec = c / sps;
-        const int id_b = __shfl_sync(0xffffffffu, id_cur, ec);
-        const int e = j * eps + ec;
-        if (ok && lane < 4 && e >= n_full && e < total) {
-          const int64_t kb32 = static_cast<int64_t>(id_b) * sps + (c % sps);
-          const uint32_t* src = bits_plane + kb32 * p.Sq + qblk * kTileM;
-          ptx::bulk_load(sBits + static_cast<uint32_t>(bst * 4 + c) * 512u, src, 512u, bar(BAR_BITS_FULL + bst));
-        }
+        if (!ok) break;
       }
-      id_cur = id_nxt; id_nxt = id_nxt2;
-      if (++st == n_stages) { st = 0; ++round; }
+      const int cb = is_k ? (p.ks[0] ? b : 0) : (p.vs[0] ? b : 0);
+      const int ch = is_k ? (p.ks[1] ? h : 0) : (p.vs[1] ? h : 0);
+      const int32_t* fids = p.full_ids + b * p.fis[0] + h * p.fis[1] + static_cast<int64_t>(qblk) * p.fis[2];
+      const int32_t* pids = p.part_ids + b * p.pis[0] + h * p.pis[1] + static_cast<int64_t>(qblk) * p.pis[2];
+      const uint32_t* bits_plane = p.bits + b * p.bits_sb + h * p.bits_sh;
+      // kv-block id of entry `lane` of step j (lanes >= entries per step hold 0)
+      auto my_id_of = [&](int j) -> int {
+        if (lane >= eps || j >= n_steps) return 0;
+        const int e = j * eps + lane;
+        const int ee = e < total ? e : 0;           // slots past the end re-load the first listed block
+        int id = ee < n_full ? fids[ee * p.fis[3]] : pids[(ee - n_full) * p.pis[3]];   // line 33
+        if (static_cast<unsigned>(id) >= static_cast<unsigned>(nk)) { bad_index = true; id = 0; }
+        return id;
+      };
+      int id_cur = my_id_of(0), id_nxt = my_id_of(1);
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const int id_nxt2 = my_id_of(j + 2);            // fetched two steps before it is needed
+        if (lane == 0) SA_TRACE_EVENT(warp, 0, j);
+        const uint32_t dst = s_tiles + st * L::kTileBytes;
+        const uint32_t full_bar = bar(bar_full + st);
+        if (lane == 0) {
+          if (round > 0) ok = ptx::mbar_wait(bar(bar_empty + st), (round - 1) & 1, abort_flag);
+          if (ok) ptx::mbar_arrive_expect_tx(full_bar, (SA_DEBUG_FLAGS & 2) ? slot_bytes : L::kTileBytes);
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (lane == 0) SA_TRACE_EVENT(warp, 1, j);
+        const int id_c = __shfl_sync(0xffffffffu, id_cur, c_of_lane & 3);
+        if (ok && c_of_lane < eps && (!(SA_DEBUG_FLAGS & 2) || lane == 0))
+          ptx::tma_load_4d(dst + pnl_of_lane * kPanelBytes + c_of_lane * slot_bytes, tm, full_bar,
+                           pnl_of_lane * 64, id_c * p.BK, ch, cb);
+        if (lane == 0) SA_TRACE_EVENT(warp, 2, j);
+        if (is_k && j >= n_plain && ok) {               // bit-mask tiles of the partial blocks of step j
+          const int u = gu + (j - n_plain), bst = u % kBitStages;
+          int n_bit_tiles = 0;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int e = j * eps + c / sps;
+            n_bit_tiles += (e >= n_full && e < total) ? 1 : 0;
+          }
+          if (lane == 0) {
+            if (u >= kBitStages) ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
+            if (ok) {
+              if (n_bit_tiles > 0) ptx::mbar_arrive_expect_tx(bar(BAR_BITS_FULL + bst), 512u * n_bit_tiles);
+              else ptx::mbar_arrive(bar(BAR_BITS_FULL + bst));
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          const int c = lane & 3, ec = c / sps;
+          const int id_b = __shfl_sync(0xffffffffu, id_cur, ec);
+          const int e = j * eps + ec;
+          if (ok && lane < 4 && e >= n_full && e < total) {
+            const int64_t kb32 = static_cast<int64_t>(id_b) * sps + (c % sps);
+            const uint32_t* src = bits_plane + kb32 * p.Sq + qblk * kTileM;
+            ptx::bulk_load(sBits + static_cast<uint32_t>(bst * 4 + c) * 512u, src, 512u, bar(BAR_BITS_FULL + bst));
+          }
+        }
+        id_cur = id_nxt; id_nxt = id_nxt2;
+        if (++st == n_stages) { st = 0; ++round; }
+      }
+      gu += n_steps - n_plain;
+      ++tq;
     }
     if (is_k && __any_sync(0xffffffffu, bad_index) && lane == 0 && p.dev_status != nullptr)
       atomicMax(p.dev_status, SA_DEV_BAD_INDEX);
     __syncwarp();
   } else if (warp == 2) {
-    // ------------------------------------------------------------------ S issuer: S(j) = Q.K(j)^T  (line 40)
+    // ------------------------------------------------------------------ S issuer: S(g) = Q.K(g)^T  (line 40)
     if (lane == 0) {
       constexpr uint32_t idesc_s = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, kTileN, 0);
       const uint64_t dq = ptx::umma_desc_sw128(sQ, 16u);
-      const uint32_t dq_lo = static_cast<uint32_t>(dq), d_hi = static_cast<uint32_t>(dq >> 32);
+      const uint32_t dq_lo0 = static_cast<uint32_t>(dq), d_hi = static_cast<uint32_t>(dq >> 32);
       const uint32_t dk_lo0 = static_cast<uint32_t>(ptx::umma_desc_sw128(sK, 16u));
-      bool ok = ptx::mbar_wait(bar(BAR_Q), 0, abort_flag);
-      int st = 0, round = 0;
-      for (int j = 0; j < n_steps && ok; ++j) {
-        SA_TRACE_EVENT(2, 0, j);
-        // Buffer j & 1 is reused: its scores were read by the softmax of step j-2 and its P by
-        // O += P.V of step j-2.  The latter implies the former, and having it complete before S(j)
-        // lets the softmax of step j write P without a wait of its own.
-        if (j >= 2) ok = ptx::mbar_wait(bar(BAR_PV_DONE + (j & 1)), ((j - 2) >> 1) & 1, abort_flag);
-        if (!ok) break;
-        SA_TRACE_EVENT(2, 1, j);
-        ok = ptx::mbar_wait(bar(BAR_K_FULL + st), round & 1, abort_flag);
-        if (!ok) break;
-        SA_TRACE_EVENT(2, 2, j);
-        ptx::tc_fence_after();
-        const uint32_t tS = tmem_base + 128u * (j & 1);
-        const uint32_t dk_lo = dk_lo0 + st * (L::kTileBytes >> 4);
+      bool ok = true;
+      int st = 0, round = 0, g = 0, tq = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+        if (ti.total == 0) continue;
+        const int qs = tq & 1;
+        ok = ptx::mbar_wait(bar(BAR_Q_FULL + qs), (tq >> 1) & 1, abort_flag);
+        const uint32_t dq_lo = dq_lo0 + qs * (L::kTileBytes >> 4);
+        for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
+          SA_TRACE_EVENT(2, 0, j);
+          // Buffer g & 1 is reused: its scores were read by the softmax of step g-2 and its P by
+          // O += P.V of step g-2.  The latter implies the former, and having it complete before S(g)
+          // lets the softmax of step g write P without a wait of its own.
+          if (g >= 2) ok = ptx::mbar_wait(bar(BAR_PV_DONE + (g & 1)), ((g - 2) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          SA_TRACE_EVENT(2, 1, j);
+          ok = ptx::mbar_wait(bar(BAR_K_FULL + st), round & 1, abort_flag);
+          if (!ok) break;
+          SA_TRACE_EVENT(2, 2, j);
+          ptx::tc_fence_after();
+          const uint32_t tS = tmem_base + 128u * (g & 1);
+          const uint32_t dk_lo = dk_lo0 + st * (L::kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          constexpr uint32_t kPanelStep = kPanelBytes >> 4;
-          const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
-          if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
-          if (kk == 0) ptx::mma_ss_lo<false>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
-          else         ptx::mma_ss_lo<true>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            constexpr uint32_t kPanelStep = kPanelBytes >> 4;
+            const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
+            if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
+            if (kk == 0) ptx::mma_ss_lo<false>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+            else         ptx::mma_ss_lo<true>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+          }
+          SA_TRACE_EVENT(2, 3, j);
+          ptx::mma_commit(bar(BAR_K_EMPTY + st));
+          ptx::mma_commit(bar(BAR_S_FULL + (g & 1)));
+          if (j == ti.n_steps - 1) ptx::mma_commit(bar(BAR_Q_EMPTY + qs));   // Q tile no longer needed
+          SA_TRACE_EVENT(2, 4, j);
+          if (++st == kStagesK) { st = 0; ++round; }
         }
-        SA_TRACE_EVENT(2, 3, j);
-        ptx::mma_commit(bar(BAR_K_EMPTY + st));
-        ptx::mma_commit(bar(BAR_S_FULL + (j & 1)));
-        SA_TRACE_EVENT(2, 4, j);
-        if (++st == kStagesK) { st = 0; ++round; }
+        ++tq;
       }
     }
     __syncwarp();
   } else if (warp == 3) {
-    // ------------------------------------------------------------------ P.V issuer: O += P(j).V(j)  (line 61)
+    // ------------------------------------------------------------------ P.V issuer: O += P(g).V(g)  (line 61)
     if (lane == 0) {
       constexpr uint32_t idesc_o = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, D, 1);
       const uint64_t dv = ptx::umma_desc_sw128(sV, kPanelBytes);
       const uint32_t dv_lo0 = static_cast<uint32_t>(dv), dv_hi = static_cast<uint32_t>(dv >> 32);
       bool ok = true;
-      for (int j = 0; j < n_steps && ok; ++j) {
-        SA_TRACE_EVENT(3, 0, j);
-        ok = ptx::mbar_wait(bar(BAR_P_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-        SA_TRACE_EVENT(3, 1, j);
-        ok = ptx::mbar_wait(bar(BAR_V_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-        SA_TRACE_EVENT(3, 2, j);
-        ptx::tc_fence_after();
-        const uint32_t tP = tmem_base + 384u + 64u * (j & 1);
-        const uint32_t dv_lo = dv_lo0 + (j & 1) * (L::kTileBytes >> 4);
-        if (j == 0) {
+      int g = 0, tq = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+        if (ti.total == 0) continue;
+        for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
+          SA_TRACE_EVENT(3, 0, j);
+          ok = ptx::mbar_wait(bar(BAR_P_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
+          if (!ok) break;
+          SA_TRACE_EVENT(3, 1, j);
+          ok = ptx::mbar_wait(bar(BAR_V_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
+          if (!ok) break;
+          // the first product of a tile overwrites O: the previous tile's epilogue must have read it
+          if (j == 0 && tq >= 1) ok = ptx::mbar_wait(bar(BAR_O_FREE), (tq - 1) & 1, abort_flag);
+          if (!ok) break;
+          SA_TRACE_EVENT(3, 2, j);
+          ptx::tc_fence_after();
+          const uint32_t tP = tmem_base + 384u + 64u * (g & 1);
+          const uint32_t dv_lo = dv_lo0 + (g & 1) * (L::kTileBytes >> 4);
+          if (j == 0) {
 #pragma unroll
-          for (int kk = 0; kk < kTileN / 16; ++kk) {
-            if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
-            if (kk == 0) ptx::mma_ts_lo<false>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
-            else         ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
-          }
-        } else {
+            for (int kk = 0; kk < kTileN / 16; ++kk) {
+              if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
+              if (kk == 0) ptx::mma_ts_lo<false>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+              else         ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+            }
+          } else {
 #pragma unroll
-          for (int kk = 0; kk < kTileN / 16; ++kk) {
-            if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
-            ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+            for (int kk = 0; kk < kTileN / 16; ++kk) {
+              if ((SA_DEBUG_FLAGS & 4) && kk > 0) break;
+              ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+            }
           }
+          SA_TRACE_EVENT(3, 3, j);
+          ptx::mma_commit(bar(BAR_V_EMPTY + (g & 1)));
+          ptx::mma_commit(bar(BAR_PV_DONE + (g & 1)));
+          if (j == ti.n_steps - 1) ptx::mma_commit(bar(BAR_O_FULL));
+          SA_TRACE_EVENT(3, 4, j);
         }
-        SA_TRACE_EVENT(3, 3, j);
-        ptx::mma_commit(bar(BAR_V_EMPTY + (j & 1)));
-        ptx::mma_commit(bar(BAR_PV_DONE + (j & 1)));
-        if (j == n_steps - 1) ptx::mma_commit(bar(BAR_O_FULL));
-        SA_TRACE_EVENT(3, 4, j);
+        ++tq;
       }
     }
     __syncwarp();
@@ -487,137 +534,159 @@ attn_fwd_tc_kernel(const AttnParams p,
     const uint32_t lane_off = static_cast<uint32_t>(lq * 32) << 16;
     const uint32_t tO_mine = tO + lane_off + kOC * quarter;
     const float scale = p.scale_log2;
-    float m = -INFINITY, l = 0.f;                  // lines 103-104; l holds this quarter's partial sum
-    bool all_finite = false;                       // every row of the warp holds a finite running max
-    for (int j = 0; j < n_steps; ++j) {
-      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 0, j);
-      ptx::mbar_wait(bar(BAR_S_FULL + (j & 1)), (j >> 1) & 1, abort_flag);
-      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 1, j);
-      ptx::tc_fence_after();
-      // this quarter's scores of buffer j & 1, and where its P goes
-      const uint32_t tS_mine = tmem_base + 128u * (j & 1) + lane_off + kCW * quarter;
-      const uint32_t tP_mine = tmem_base + 384u + 64u * (j & 1) + lane_off + (kCW / 2) * quarter;
-      const bool masked = j >= n_plain;
-      uint32_t w[kCW / 32];
+    int g0 = 0, gu = 0, tq = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+      const int n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps, n_plain = ti.n_plain;
+      T* o_base = static_cast<T*>(p.o) + ti.b * p.os[0] + ti.h * p.os[1] +
+                  static_cast<int64_t>(ti.qblk) * kTileM * p.os[2];
+      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + kOC * quarter);
+      if (total == 0) {                            // nothing attended: the rows are 0
 #pragma unroll
-      for (int c = 0; c < kCW / 32; ++c) w[c] = 0xffffffffu;
-      if (masked) {
-        const int u = j - n_plain, st = u % kBitStages;
-        ptx::mbar_wait(bar(BAR_BITS_FULL + st), (u / kBitStages) & 1, abort_flag);
-#pragma unroll
-        for (int c = 0; c < kCW / 32; ++c) {
-          const int ss = quarter * (kCW / 32) + c;           // sub-slot of the step
-          const int e = j * eps + ss / sps;
-          w[c] = e < n_full ? 0xffffffffu : (e < total ? bits_smem[(st * 4 + ss) * 128 + row] : 0u);
-        }
-        ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
-      }
-      float* xch_mine = xch + ((j & 1) * kSplit + quarter) * 128 + row;
-      const float* xch_row = xch + (j & 1) * kSplit * 128 + row;
-      auto row_max = [&]() {
-        float v = xch_row[0];
-#pragma unroll
-        for (int g = 1; g < kSplit; ++g) v = fmaxf(v, xch_row[128 * g]);
-        return v;
-      };
-      if (SA_DEBUG_FLAGS & 1) {
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(bar(BAR_P_FULL + (j & 1)));
+        for (int i = 0; i < kOC / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
         continue;
       }
-      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 2, j);
-
-      // Rows that already hold a finite running max exponentiate against it straight away
-      // (one pass); the max only moves when a score exceeds it by more than the threshold.
-      if (!all_finite) all_finite = !__any_sync(0xffffffffu, m == -INFINITY);
-      const bool slow = !all_finite;
-      float m_new = m, alpha = 1.f, m_ref = m;
-      bool second_pass = true;
-      if (!slow) {
-        float sum, xmax;
-        if (SA_DEBUG_FLAGS & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m, w, sum, xmax);
-        else if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
-        else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
-        *xch_mine = xmax;
-        ptx::named_bar_sync(1 + lq, 32 * kSplit);
-        const float xrow = row_max();
-        if (!__any_sync(0xffffffffu, xrow > kRescaleThreshold)) {
-          l += sum;
-          second_pass = false;
-        } else if (xrow > kRescaleThreshold) {
-          m_new = m + xrow;
-          alpha = ex2_approx(-xrow);                              // exp2(m - m_new), line 55
-          m_ref = m_new;
-        }
-      } else {
-        float smax;
-        if (masked) max_pass<true, kCW>(tS_mine, w, smax);
-        else        max_pass<false, kCW>(tS_mine, w, smax);
-        *xch_mine = smax;
-        ptx::named_bar_sync(1 + lq, 32 * kSplit);
-        const float srow = row_max();
-        const float m_tile = srow * scale;                        // lines 48 / 50
-        const float m_cand = fmaxf(m, m_tile);
-        if (m == -INFINITY) { m_new = m_cand; }                   // nothing accumulated yet
-        else if (m_cand > m + kRescaleThreshold) { m_new = m_cand; alpha = ex2_approx(m - m_new); }
-        m_ref = (m_new == -INFINITY) ? 0.f : m_new;               // guard the reference lacks (line 53)
-      }
-      if (second_pass) {
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this thread's O columns
-          // O must hold every product up to step j-1 before it is rescaled.  P.V(j-2) completed
-          // before S(j) was issued, so this barrier is at most one phase behind.
-          ptx::mbar_wait(bar(BAR_PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
-          ptx::tc_fence_after();
+      float m = -INFINITY, l = 0.f;                // lines 103-104; l holds this group's partial sum
+      bool all_finite = false;                     // every row of the warp holds a finite running max
+      for (int j = 0; j < n_steps; ++j) {
+        const int g = g0 + j;                      // steps since the kernel started: buffer and phase
+        if (threadIdx.x == 128) SA_TRACE_EVENT(4, 0, j);
+        ptx::mbar_wait(bar(BAR_S_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
+        if (threadIdx.x == 128) SA_TRACE_EVENT(4, 1, j);
+        ptx::tc_fence_after();
+        // this group's scores of buffer g & 1, and where its P goes
+        const uint32_t tS_mine = tmem_base + 128u * (g & 1) + lane_off + kCW * quarter;
+        const uint32_t tP_mine = tmem_base + 384u + 64u * (g & 1) + lane_off + (kCW / 2) * quarter;
+        const bool masked = j >= n_plain;
+        uint32_t w[kCW / 32];
 #pragma unroll
-          for (int c = 0; c < kOC / kOChunk; ++c) {
-            uint32_t r[kOChunk];
-            tmem_load_cols<kOChunk>(tO_mine + c * kOChunk, r);
-            ptx::tmem_ld_wait();
+        for (int c = 0; c < kCW / 32; ++c) w[c] = 0xffffffffu;
+        if (masked) {
+          const int u = gu + (j - n_plain), st = u % kBitStages;
+          ptx::mbar_wait(bar(BAR_BITS_FULL + st), (u / kBitStages) & 1, abort_flag);
 #pragma unroll
-            for (int i = 0; i < kOChunk; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_store_cols<kOChunk>(tO_mine + c * kOChunk, r);
+          for (int c = 0; c < kCW / 32; ++c) {
+            const int ss = quarter * (kCW / 32) + c;           // sub-slot of the step
+            const int e = j * eps + ss / sps;
+            w[c] = e < n_full ? 0xffffffffu : (e < total ? bits_smem[(st * 4 + ss) * 128 + row] : 0u);
           }
+          ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
         }
-        float sum, xmax;
-        if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
-        else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
-        l = l * alpha + sum;                                      // line 57
-        m = m_new;                                                // line 56
-      }
-      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 3, j);
-      ptx::tmem_st_wait();
-      ptx::tc_fence_before();
-      ptx::mbar_arrive(bar(BAR_P_FULL + (j & 1)));
-      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 4, j);
-    }
-    ptx::mbar_wait(bar(BAR_O_FULL), 0, abort_flag);
-    // A wait that ran out leaves the abort flag set; nothing is written in that case.
-    float* xch_mine = xch + ((n_steps & 1) * kSplit + quarter) * 128 + row;
-    const float* xch_row = xch + (n_steps & 1) * kSplit * 128 + row;
-    *xch_mine = l;
-    ptx::named_bar_sync(1 + lq, 32 * kSplit);
-    if (*abort_flag == 0) {
-      ptx::tc_fence_after();
-      float l_row = xch_row[0];
+        float* xch_mine = xch + ((g & 1) * kSplit + quarter) * 128 + row;
+        const float* xch_row = xch + (g & 1) * kSplit * 128 + row;
+        auto row_max = [&]() {
+          float v = xch_row[0];
 #pragma unroll
-      for (int g = 1; g < kSplit; ++g) l_row += xch_row[128 * g];
-      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;          // line 144, with 0 for an empty row
-      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + kOC * quarter);
+          for (int q = 1; q < kSplit; ++q) v = fmaxf(v, xch_row[128 * q]);
+          return v;
+        };
+        if (SA_DEBUG_FLAGS & 1) {
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(bar(BAR_P_FULL + (g & 1)));
+          continue;
+        }
+        if (threadIdx.x == 128) SA_TRACE_EVENT(4, 2, j);
+
+        // Rows that already hold a finite running max exponentiate against it straight away
+        // (one pass); the max only moves when a score exceeds it by more than the threshold.
+        if (!all_finite) all_finite = !__any_sync(0xffffffffu, m == -INFINITY);
+        const bool slow = !all_finite;
+        float m_new = m, alpha = 1.f, m_ref = m;
+        bool second_pass = true;
+        if (!slow) {
+          float sum, xmax;
+          if (SA_DEBUG_FLAGS & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m, w, sum, xmax);
+          else if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
+          else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
+          *xch_mine = xmax;
+          ptx::named_bar_sync(1 + lq, 32 * kSplit);
+          const float xrow = row_max();
+          if (!__any_sync(0xffffffffu, xrow > kRescaleThreshold)) {
+            l += sum;
+            second_pass = false;
+          } else if (xrow > kRescaleThreshold) {
+            m_new = m + xrow;
+            alpha = ex2_approx(-xrow);                              // exp2(m - m_new), line 55
+            m_ref = m_new;
+          }
+        } else {
+          float smax;
+          if (masked) max_pass<true, kCW>(tS_mine, w, smax);
+          else        max_pass<false, kCW>(tS_mine, w, smax);
+          *xch_mine = smax;
+          ptx::named_bar_sync(1 + lq, 32 * kSplit);
+          const float srow = row_max();
+          const float m_tile = srow * scale;                        // lines 48 / 50
+          const float m_cand = fmaxf(m, m_tile);
+          if (m == -INFINITY) { m_new = m_cand; }                   // nothing accumulated yet
+          else if (m_cand > m + kRescaleThreshold) { m_new = m_cand; alpha = ex2_approx(m - m_new); }
+          m_ref = (m_new == -INFINITY) ? 0.f : m_new;               // guard the reference lacks (line 53)
+        }
+        if (second_pass) {
+          if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this thread's O columns
+            // O must hold every product up to step g-1 before it is rescaled.  P.V(g-2) completed
+            // before S(g) was issued, so this barrier is at most one phase behind.
+            ptx::mbar_wait(bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag);
+            ptx::tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < kOC / kOChunk; ++c) {
+              uint32_t r[kOChunk];
+              tmem_load_cols<kOChunk>(tO_mine + c * kOChunk, r);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < kOChunk; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_store_cols<kOChunk>(tO_mine + c * kOChunk, r);
+            }
+          }
+          float sum, xmax;
+          if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
+          else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
+          l = l * alpha + sum;                                      // line 57
+          m = m_new;                                                // line 56
+        }
+        if (threadIdx.x == 128) SA_TRACE_EVENT(4, 3, j);
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar(BAR_P_FULL + (g & 1)));
+        if (threadIdx.x == 128) SA_TRACE_EVENT(4, 4, j);
+      }
+      // ---- epilogue of the tile: O / l.  The row sums of the column groups meet in a buffer of their
+      // own (the per-step exchange buffers may already be in use by the next tile's first step).
+      ptx::mbar_wait(bar(BAR_O_FULL), tq & 1, abort_flag);
+      ptx::tc_fence_after();
+      float* xl = xch + 2 * kSplit * 128;
+      xl[quarter * 128 + row] = l;
+      ptx::named_bar_sync(1 + lq, 32 * kSplit);
+      float l_row = xl[row];
+#pragma unroll
+      for (int q = 1; q < kSplit; ++q) l_row += xl[128 * q + row];
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;            // line 144, with 0 for an empty row
+      uint32_t ro[kOC];
 #pragma unroll
       for (int c = 0; c < kOC / kOChunk; ++c) {
         uint32_t r[kOChunk];
         tmem_load_cols<kOChunk>(tO_mine + c * kOChunk, r);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < kOChunk / 8; ++i) {
+        for (int i = 0; i < kOChunk; ++i) ro[c * kOChunk + i] = r[i];
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(bar(BAR_O_FREE));                            // O may be overwritten by the next tile
+      // A wait that ran out leaves the abort flag set; nothing is written in that case.
+      if (*abort_flag == 0) {
+#pragma unroll
+        for (int i = 0; i < kOC / 8; ++i) {
           uint4 v;
-          v.x = Fmt<T>::pack2(__uint_as_float(r[8 * i + 0]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
-          v.y = Fmt<T>::pack2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
-          v.z = Fmt<T>::pack2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
-          v.w = Fmt<T>::pack2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-          dst[c * (kOChunk / 8) + i] = v;                 // line 146
+          v.x = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 0]) * inv, __uint_as_float(ro[8 * i + 1]) * inv);
+          v.y = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 2]) * inv, __uint_as_float(ro[8 * i + 3]) * inv);
+          v.z = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 4]) * inv, __uint_as_float(ro[8 * i + 5]) * inv);
+          v.w = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 6]) * inv, __uint_as_float(ro[8 * i + 7]) * inv);
+          dst[i] = v;                                               // line 146
         }
       }
+      g0 += n_steps;
+      gu += n_steps - n_plain;
+      ++tq;
     }
   }
 
@@ -694,8 +763,17 @@ int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& m
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(Smem<D>::dynamic_bytes));
   if (e != cudaSuccess) return SA_ERR_CUDA;
-  dim3 grid(p.Sq / kTileM, p.B * p.H);
-  kernel<<<grid, kThreadsTC, Smem<D>::dynamic_bytes, stream>>>(p, mq, mk, mv);
+  const int n_tiles = (p.Sq / kTileM) * p.B * p.H;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return SA_ERR_CUDA;
+    sm_count = sms;
+  }
+  const int grid = n_tiles < sm_count ? n_tiles : sm_count;    // persistent: one CTA per SM walks the tiles
+  kernel<<<grid, kThreadsTC, Smem<D>::dynamic_bytes, stream>>>(p, mq, mk, mv, n_tiles);
   return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 
