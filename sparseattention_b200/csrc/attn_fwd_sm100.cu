@@ -148,16 +148,46 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 
-// One pass over this thread's kCW score columns (kCW / 32 TMEM loads): x = s*scale - m_ref, masked
-// columns -> -inf, P = exp2(x) rounded to T and written to the kCW / 2 columns at t_p, fp32 row sum
-// of the unrounded P (lines 54, 57, 61) and max of x.  w[c] is the bit-mask word of columns 32c..32c+31.
+// 32 score columns of one thread: x = s*scale - m_ref, masked columns -> -inf (kMasked), P = exp2(x)
+// rounded to T into pk, fp32 sum of the unrounded P (lines 54, 57, 61) and max of x.
+template <typename T, bool kMasked, int kPolyEvery, bool kNoExp>
+__device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t w, uint64_t scale2, uint64_t nm2,
+                                              uint32_t (&pk)[16], uint64_t& sum2, float& xmax) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float x0, x1;
+    ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_u32x2(r[2 * i], r[2 * i + 1]), scale2, nm2), x0, x1);
+    if (kMasked) {
+      x0 = (w >> (2 * i)) & 1u ? x0 : -INFINITY;                 // line 47
+      x1 = (w >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
+    }
+    xmax = ptx::max3(xmax, x0, x1);
+    float p0, p1;
+    if (kNoExp) { p0 = x0 * x1; p1 = x1 * x0; }
+    else if (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1)
+      ptx::exp2_poly_pair(x0, x1, p0, p1);
+    else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
+    sum2 = ptx::add_f32x2(sum2, ptx::pack_f32x2(p0, p1));
+    pk[i] = Fmt<T>::pack2(p0, p1);
+  }
+}
+
+// One pass over this thread's kCW score columns, kCW / 32 chunks of 32.  w[c] is the bit-mask word
+// of chunk c for this thread's row; a warp covers 32 rows, so on masked steps a chunk is one 32 x 32
+// block of the mask.  A block that is False for all 32 rows costs no arithmetic (P = 0, no
+// exponentials).  (A third, mask-free variant for all-True blocks made the loop body large enough
+// to lose more than it won.)
 template <typename T, bool kMasked, int kPolyEvery, int kCW, bool kNoExp = false>
 __device__ __forceinline__ void softmax_pass(uint32_t t_s, uint32_t t_p, float scale, float m_ref,
                                              const uint32_t (&w)[kCW / 32], float& sum_out, float& xmax_out) {
   constexpr int kChunks = kCW / 32;
+  bool dead[kChunks];
   uint32_t r[kChunks][32];
 #pragma unroll
-  for (int c = 0; c < kChunks; ++c) ptx::tmem_ld32(t_s + 32 * c, r[c]);
+  for (int c = 0; c < kChunks; ++c) {
+    dead[c] = kMasked && __all_sync(0xffffffffu, w[c] == 0u);
+    ptx::tmem_ld32(t_s + 32 * c, r[c]);
+  }
   ptx::tmem_ld_wait();
   const uint64_t scale2 = ptx::pack_f32x2(scale, scale);
   const uint64_t nm2 = ptx::pack_f32x2(-m_ref, -m_ref);
@@ -166,22 +196,11 @@ __device__ __forceinline__ void softmax_pass(uint32_t t_s, uint32_t t_p, float s
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     uint32_t pk[16];
+    if (dead[c]) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float x0, x1;
-      ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_u32x2(r[c][2 * i], r[c][2 * i + 1]), scale2, nm2), x0, x1);
-      if (kMasked) {
-        x0 = (w[c] >> (2 * i)) & 1u ? x0 : -INFINITY;                 // line 47
-        x1 = (w[c] >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
-      }
-      xmax = ptx::max3(xmax, x0, x1);
-      float p0, p1;
-      if (kNoExp) { p0 = x0 * x1; p1 = x1 * x0; }
-      else if (kPolyEvery > 0 && ((c * 16 + i) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1)
-        ptx::exp2_poly_pair(x0, x1, p0, p1);
-      else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
-      sum2 = ptx::add_f32x2(sum2, ptx::pack_f32x2(p0, p1));
-      pk[i] = Fmt<T>::pack2(p0, p1);
+      for (int i = 0; i < 16; ++i) pk[i] = 0u;
+    } else {
+      softmax_chunk<T, kMasked, kPolyEvery, kNoExp>(r[c], w[c], scale2, nm2, pk, sum2, xmax);
     }
     ptx::tmem_st16(t_p + 16 * c, pk);
   }
@@ -191,6 +210,20 @@ __device__ __forceinline__ void softmax_pass(uint32_t t_s, uint32_t t_p, float s
   xmax_out = xmax;
 }
 
+// The same pass out of line, for the rare second pass after the running max moved (keeps the hot
+// loop's code small).
+template <typename T, bool kMasked, int kPolyEvery, int kCW>
+__device__ __noinline__ void softmax_pass_cold(uint32_t t_s, uint32_t t_p, float scale, float m_ref,
+                                               uint32_t w0, uint32_t w1, float* sum_out, float* xmax_out) {
+  uint32_t w[kCW / 32];
+  w[0] = w0;
+  if (kCW / 32 > 1) w[kCW / 32 - 1] = w1;
+  float sum, xmax;
+  softmax_pass<T, kMasked, kPolyEvery, kCW>(t_s, t_p, scale, m_ref, w, sum, xmax);
+  *sum_out = sum;
+  *xmax_out = xmax;
+}
+
 // Max of the raw (masked) scores of this thread's kCW columns.
 template <bool kMasked, int kCW>
 __device__ __forceinline__ void max_pass(uint32_t t_s, const uint32_t (&w)[kCW / 32], float& smax_out) {
@@ -198,6 +231,7 @@ __device__ __forceinline__ void max_pass(uint32_t t_s, const uint32_t (&w)[kCW /
   float mx = -INFINITY;
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
+    if (kMasked && __all_sync(0xffffffffu, w[c] == 0u)) continue;     // block masked for all 32 rows
     uint32_t r[32];
     ptx::tmem_ld32(t_s + 32 * c, r);
     ptx::tmem_ld_wait();
@@ -639,8 +673,9 @@ attn_fwd_tc_kernel(const AttnParams p,
             }
           }
           float sum, xmax;
-          if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
-          else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m_ref, w, sum, xmax);
+          static_assert(kCW / 32 <= 2, "the out-of-line pass takes two mask words");
+          softmax_pass_cold<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_ref, w[0], w[kCW / 32 - 1],
+                                                       &sum, &xmax);
           l = l * alpha + sum;                                      // line 57
           m = m_new;                                                // line 56
         }
