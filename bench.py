@@ -337,11 +337,12 @@ def run_ours(args):
                        "shard": "each rank owns a full (batch, head) shard of the workload"},
             "roofline": {"bound": "tensor", "achieved": att_tflops, "peak": peaks["bf16_tflops_sustained"],
                          "unit": "TFLOP/s", "frac": att_tflops / peaks["bf16_tflops_sustained"],
-                         "traffic": 254.65e6 * B / 2.0, "traffic_unit": "bytes per launch (ncu capture at B=2, p=0.5, scaled by batch)",
+                         "traffic": 256.7e6 * B / 2.0, "traffic_unit": "bytes per launch (ncu capture at B=2, p=0.5, scaled by batch)",
                          "kernel": "attn_fwd_tc_kernel<bf16,128>", "peak_source": peak_kind + " (sustained bf16 matmul)",
                          "note": "FLOPs of the listed tiles of all six launches / sum of their durations (CUDA events)"},
             "roofline_classifier": {"bound": "hbm", "achieved": cls_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                    "frac": cls_gbs / peaks["hbm_gbs"], "traffic": None,
+                                    "frac": cls_gbs / peaks["hbm_gbs"], "traffic": 276.7e6 * B / 16.0,
+                                    "traffic_unit": "bytes per launch (ncu capture at 16 planes, scaled by planes)",
                                     "kernel": "classify_cells_kernel + compact_lists_kernel",
                                     "note": "algorithmic bytes / duration of the whole stage-1 call incl. its allocations"},
             "sweep": [{"p": p, "classify_ms": c, "attn_ms": a, "attn_tflops": fl / (a * 1e-3) / 1e12,
