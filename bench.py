@@ -210,13 +210,14 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     _native.load_library()        # fail loudly if the CUDA library is missing
 
-    cfg = workloads.CONFIGS["headline"]
+    cfg = workloads.CONFIGS[args.workload]
     B, H, S, D = (args.batch or cfg.B), cfg.H, cfg.S, cfg.D
     ps = [float(x) for x in args.ps.split(",")] if args.ps else list(cfg.drop_ps)
     dtype = torch.bfloat16
     warmup = args.warmup if args.profile else max(args.warmup, 3)
     q, k, v = workloads.make_qkv(B, H, S, D, dtype, seed=1000 + rank, device=dev)
-    masks = [workloads.random_block_mask(B, S, p, cfg.partial_frac, seed=2000 + 17 * rank + i, device=dev)
+    planes = 1 if cfg.mask_batch == 1 else B                    # distinct mask planes (the composed mask is shared)
+    masks = [workloads.make_mask(cfg, p, seed=2000 + 17 * rank + i, device=dev, batch=planes)
              for i, p in enumerate(ps)]
     masks_e = [m.expand(B, H, S, S) for m in masks]
 
@@ -233,7 +234,7 @@ def run_ours(args):
         o = sa.sparse_attention(q, k, v, masks[i], BQ, BK, mask_metadata=md, impl="tcgen05", check_status=True)
         flops_p.append(workloads.computed_tile_flops(md.unmasked_lens, md.masked_lens, BQ, BK, D))
         lens_sum = int(md.unmasked_lens[:, 0].sum()) + int(md.masked_lens[:, 0].sum())
-        bytes_p.append(workloads.classifier_bytes(B, S, S, BQ, lens_sum))
+        bytes_p.append(workloads.classifier_bytes(planes, S, S, BQ, lens_sum))
         tiles = B * H * (S // BQ) * (S // BK)
         mix.append((float(md.unmasked_lens.sum()) / tiles, float(md.masked_lens.sum()) / tiles))
         del o, md
@@ -279,11 +280,16 @@ def run_ours(args):
     att_ms = [statistics.mean(ev[s][2 * i + 1].elapsed_time(ev[s][2 * i + 2]) for s in range(args.steps)) for i in range(n_p)]
 
     # ---- end to end through the public entry points with host buffers
-    if args.profile:
+    if args.profile or args.workload != "headline":
         if world > 1:
             torch.distributed.destroy_process_group()
         if rank == 0:
-            print(json.dumps({"profile_run": True, "classify_ms": cls_ms, "attn_ms": att_ms, "B": B, "ps": ps}))
+            print(json.dumps({"profile_run": bool(args.profile), "workload": args.workload, "B": B, "ps": ps,
+                              "classify_ms": cls_ms, "attn_ms": att_ms,
+                              "attn_tflops": [f / (a * 1e-3) / 1e12 for f, a in zip(flops_p, att_ms)],
+                              "classify_gbs": [by / (c * 1e-3) / 1e9 for by, c in zip(bytes_p, cls_ms)],
+                              "tile_mix_full_partial": mix,
+                              "effective_tflops_both_stages": flops_step / (elapsed_ms / args.steps * 1e-3) / 1e12}))
         return
     host_q, host_k, host_v = (t.cpu().pin_memory() for t in (q, k, v))
     host_masks = [m.cpu().pin_memory() for m in masks]
@@ -380,6 +386,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="profiling run: kernels only (no end-to-end leg, no CPU baseline, no warm-up floor)")
+    ap.add_argument("--workload", default="headline", choices=["headline", "document", "composed", "scaling"],
+                    help="headline = the benchmark line; the others print kernel-only figures for that configuration")
     ap.add_argument("--batch", type=int, default=0, help="profiling: override the batch size of the workload")
     ap.add_argument("--ps", default="", help="profiling: comma-separated subset of the drop probabilities")
     args = ap.parse_args()
