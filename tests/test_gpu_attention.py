@@ -169,3 +169,17 @@ def test_headline_shape_slice(native_lib):
     simt = sa.sparse_attention(q, k, v, mask, 128, 32, mask_metadata=md, impl="simt", check_status=True)
     d = (out.float() - simt.float()).abs()
     assert d.max().item() <= MAX_ABS_16 and d.mean().item() <= 2e-3
+
+
+def test_custom_ops_pass_opcheck(native_lib):
+    """The two torch.library ops: schema and fake-tensor (shape / dtype propagation) checks."""
+    B, H, S, D = 1, 2, 256, 128
+    q, k, v = (t.to(DEV) for t in workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=11))
+    mask = workloads.random_block_mask(B, S, 0.5, 0.2, seed=11).to(DEV)
+    checks = ("test_schema", "test_faketensor")
+    torch.library.opcheck(_native.classify_mask_op, (mask, 128, 32, True), test_utils=checks)
+    f_ids, f_lens, p_ids, p_lens, bits = _native.classify(mask, 128, 32)
+    ex = lambda t, nd: t.expand(*((B, H) + tuple(t.shape[2:])))
+    args = (q, k, v, mask.expand(B, H, S, S), bits, ex(f_ids, 4), ex(f_lens, 3), ex(p_ids, 4), ex(p_lens, 3),
+            128, 32, _native.SA_IMPL_AUTO, False)
+    torch.library.opcheck(_native.attn_fwd_op, args, test_utils=checks)
