@@ -19,13 +19,14 @@
 //              (tcgen05.mma, both operands in shared memory), one step ahead of the softmax.
 //   warp 3     P.V issuer.  O += P(j).V(j) with P read from its own buffer in tensor memory.
 //   warps 4-11 softmax; a thread owns a query row and one half of the 128 score columns.  Scores
-//              are exponentiated against the row's running max in a single pass (base 2, scale
-//              folded as in sparse_attn_kernel.py:152); the max moves, and O is rescaled in
-//              tensor memory, only when a score exceeds it by more than 2^8 (the pass is then
-//              redone from the intact scores).  Steps that contain a partial or padding block apply
+//              are exponentiated against the row's running reference max in a single pass (base 2,
+//              scale folded as in sparse_attn_kernel.py:152; a row's first scores are tried against
+//              0); the reference moves, and O is rescaled in tensor memory, only when a score
+//              exceeds it by more than 2^8 (the pass is then redone from the intact scores).  Steps that contain a partial or padding block apply
 //              the bit mask; steps of full blocks do no mask work.  P is rounded to the V dtype
-//              (line 61); row sums stay in fp32 (line 57).  Finally O / l is written; a row with no
-//              attended key yields 0 (the reference yields NaN, line 53).
+//              (line 61); row sums stay in fp32 (line 57).  Finally O / l is staged in the tile's Q
+//              slot and written with one TMA store per warp; a row with no attended key yields 0
+//              (the reference yields NaN, line 53).
 //
 // Tensor memory (512 columns): score buffers at 0 and 128, O at 256, P buffers at 384 and 448.
 //
@@ -56,6 +57,7 @@ constexpr int kStagesV = 2;          // V tiles in flight in shared memory
 constexpr int kBitStages = 4;        // steps of bit-mask tiles in flight
 constexpr uint32_t kPanelBytes = 128u * 128u;   // 128 rows x 64 elements x 2 B
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
+constexpr float kFreshFloor = -4.0f;            // a row's first scores are taken against 0 if their max is in [-4, 8]
 #ifndef SA_POLY_PLAIN
 #define SA_POLY_PLAIN 0
 #endif
@@ -79,7 +81,8 @@ enum Bar : int {
   BAR_O_FREE,                                      // the epilogue has read O out of tensor memory
   BAR_BITS_FULL,                                   // kBitStages
   BAR_BITS_EMPTY = BAR_BITS_FULL + kBitStages,
-  BAR_COUNT = BAR_BITS_EMPTY + kBitStages
+  BAR_Q_STORED = BAR_BITS_EMPTY + kBitStages,      // 2: the O tile staged in the Q slot has been read by its store
+  BAR_COUNT = BAR_Q_STORED + 2
 };
 
 template <int D>
@@ -224,30 +227,6 @@ __device__ __noinline__ void softmax_pass_cold(uint32_t t_s, uint32_t t_p, float
   *xmax_out = xmax;
 }
 
-// Max of the raw (masked) scores of this thread's kCW columns.
-template <bool kMasked, int kCW>
-__device__ __forceinline__ void max_pass(uint32_t t_s, const uint32_t (&w)[kCW / 32], float& smax_out) {
-  constexpr int kChunks = kCW / 32;
-  float mx = -INFINITY;
-#pragma unroll
-  for (int c = 0; c < kChunks; ++c) {
-    if (kMasked && __all_sync(0xffffffffu, w[c] == 0u)) continue;     // block masked for all 32 rows
-    uint32_t r[32];
-    ptx::tmem_ld32(t_s + 32 * c, r);
-    ptx::tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float a0 = __uint_as_float(r[2 * i]), a1 = __uint_as_float(r[2 * i + 1]);
-      if (kMasked) {
-        a0 = (w[c] >> (2 * i)) & 1u ? a0 : -INFINITY;
-        a1 = (w[c] >> (2 * i + 1)) & 1u ? a1 : -INFINITY;
-      }
-      mx = ptx::max3(mx, a0, a1);
-    }
-  }
-  smax_out = mx;
-}
-
 // Moves kCols fp32 columns between tensor memory and registers (kCols = 32 or 16).
 template <int kCols>
 __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&r)[kCols]) {
@@ -264,7 +243,8 @@ struct TileInfo {
   int n_full, n_part, total, n_steps, n_plain;
 };
 
-__device__ __forceinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq, int nk, int eps) {
+// Out of line: every role calls it once per tile, and one copy keeps the kernel's code small.
+__device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq, int nk, int eps_shift) {
   TileInfo t;
   const int bh = tile / nq;
   t.qblk = tile % nq;
@@ -275,17 +255,18 @@ __device__ __forceinline__ TileInfo tile_info(const AttnParams& p, int tile, int
   t.n_full = min(max(n_full, 0), nk);
   t.n_part = min(max(n_part, 0), nk);
   t.total = t.n_full + t.n_part;
-  t.n_steps = (t.total + eps - 1) / eps;
-  t.n_plain = t.n_full / eps;          // leading steps made of full blocks only
+  t.n_steps = (t.total + (1 << eps_shift) - 1) >> eps_shift;
+  t.n_plain = t.n_full >> eps_shift;   // leading steps made of full blocks only
   return t;
 }
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreadsTC, 1)
-attn_fwd_tc_kernel(const AttnParams p,
+attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
                    const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_o,
                    const int n_tiles) {
   using L = Smem<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -306,10 +287,20 @@ attn_fwd_tc_kernel(const AttnParams p,
   long long* trace_buf = reinterpret_cast<long long*>(smem + L::total);
   if (trace_on) for (int i = threadIdx.x; i < 5 * kTraceCap; i += blockDim.x) trace_buf[i] = 0;
 #endif
+  // The epilogue stages a tile of O in the Q slot it has finished with and stores it with TMA when a
+  // thread's share of a row is one 128-byte swizzle row; otherwise the threads store their rows directly.
+#ifdef SA_NO_STAGE_O
+  constexpr bool kStageO = false;
+#else
+  constexpr bool kStageO = (D / kSplit) * sizeof(T) == 128;
+#endif
   const int nq = p.Sq / kTileM;
   const int nk = p.Sk / p.BK;
-  const int eps = kTileN / p.BK;        // list entries per step
-  const int sps = p.BK / 32;            // 32-column sub-slots per entry
+  // BLOCK_K is 32, 64 or 128: list entries per step (4, 2, 1) and 32-column sub-slots per entry
+  // (1, 2, 4) are powers of two, so the per-step index arithmetic is shifts.
+  const int eps_shift = p.BK == 32 ? 2 : (p.BK == 64 ? 1 : 0);
+  const int sps_shift = 2 - eps_shift;
+  const int eps = 1 << eps_shift;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -318,6 +309,7 @@ attn_fwd_tc_kernel(const AttnParams p,
       ptx::mbar_init(bar(BAR_S_FULL + i), 1);
       ptx::mbar_init(bar(BAR_P_FULL + i), 128 * kSplit);
       ptx::mbar_init(bar(BAR_PV_DONE + i), 1);
+      ptx::mbar_init(bar(BAR_Q_STORED + i), 4 * kSplit);
     }
     for (int i = 0; i < kStagesK; ++i) {
       ptx::mbar_init(bar(BAR_K_FULL + i), 1);
@@ -372,14 +364,17 @@ attn_fwd_tc_kernel(const AttnParams p,
     bool ok = true;
     int st = 0, round = 0, gu = 0, tq = 0;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+      const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
       if (ti.total == 0) continue;
       const int b = ti.b, h = ti.h, qblk = ti.qblk, n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps,
                 n_plain = ti.n_plain;
       if (is_k) {                                   // Q tile of this query block, double-buffered
         const int qs = tq & 1;
         if (lane == 0) {
-          if (tq >= 2) ok = ptx::mbar_wait(bar(BAR_Q_EMPTY + qs), ((tq >> 1) - 1) & 1, abort_flag);
+          if (tq >= 2) {
+            ok = ptx::mbar_wait(bar(BAR_Q_EMPTY + qs), ((tq >> 1) - 1) & 1, abort_flag);
+            if (ok && kStageO) ok = ptx::mbar_wait(bar(BAR_Q_STORED + qs), ((tq >> 1) - 1) & 1, abort_flag);
+          }
           if (ok) {
             const int qb = p.qs[0] ? b : 0, qh = p.qs[1] ? h : 0;
             ptx::mbar_arrive_expect_tx(bar(BAR_Q_FULL + qs), L::kTileBytes);
@@ -400,7 +395,7 @@ attn_fwd_tc_kernel(const AttnParams p,
       // kv-block id of entry `lane` of step j (lanes >= entries per step hold 0)
       auto my_id_of = [&](int j) -> int {
         if (lane >= eps || j >= n_steps) return 0;
-        const int e = j * eps + lane;
+        const int e = (j << eps_shift) + lane;
         const int ee = e < total ? e : 0;           // slots past the end re-load the first listed block
         int id = ee < n_full ? fids[ee * p.fis[3]] : pids[(ee - n_full) * p.pis[3]];   // line 33
         if (static_cast<unsigned>(id) >= static_cast<unsigned>(nk)) { bad_index = true; id = 0; }
@@ -428,7 +423,7 @@ attn_fwd_tc_kernel(const AttnParams p,
           int n_bit_tiles = 0;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const int e = j * eps + c / sps;
+            const int e = (j << eps_shift) + (c >> sps_shift);
             n_bit_tiles += (e >= n_full && e < total) ? 1 : 0;
           }
           if (lane == 0) {
@@ -439,11 +434,11 @@ attn_fwd_tc_kernel(const AttnParams p,
             }
           }
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-          const int c = lane & 3, ec = c / sps;
+          const int c = lane & 3, ec = c >> sps_shift;
           const int id_b = __shfl_sync(0xffffffffu, id_cur, ec);
-          const int e = j * eps + ec;
+          const int e = (j << eps_shift) + ec;
           if (ok && lane < 4 && e >= n_full && e < total) {
-            const int64_t kb32 = static_cast<int64_t>(id_b) * sps + (c % sps);
+            const int64_t kb32 = (static_cast<int64_t>(id_b) << sps_shift) + (c & ((1 << sps_shift) - 1));
             const uint32_t* src = bits_plane + kb32 * p.Sq + qblk * kTileM;
             ptx::bulk_load(sBits + static_cast<uint32_t>(bst * 4 + c) * 512u, src, 512u, bar(BAR_BITS_FULL + bst));
           }
@@ -467,7 +462,7 @@ attn_fwd_tc_kernel(const AttnParams p,
       bool ok = true;
       int st = 0, round = 0, g = 0, tq = 0;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+        const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
         if (ti.total == 0) continue;
         const int qs = tq & 1;
         ok = ptx::mbar_wait(bar(BAR_Q_FULL + qs), (tq >> 1) & 1, abort_flag);
@@ -514,7 +509,7 @@ attn_fwd_tc_kernel(const AttnParams p,
       bool ok = true;
       int g = 0, tq = 0;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+        const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
         if (ti.total == 0) continue;
         for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
           SA_TRACE_EVENT(3, 0, j);
@@ -569,9 +564,25 @@ attn_fwd_tc_kernel(const AttnParams p,
     const uint32_t tO_mine = tO + lane_off + kOC * quarter;
     const float scale = p.scale_log2;
     int g0 = 0, gu = 0, tq = 0;
+    int stored_slot = -1;                          // Q slot holding a staged O tile whose store is in flight
+    if (kStageO && warp == kSoftmaxWarp0 && lane == 0) ptx::prefetch_tensormap(&tm_o);
+    // The store of the previous tile has had the tile-info loads to read its shared-memory source; the
+    // producer may then reuse the slot for the Q tile after next.
+    auto release_staged = [&]() {
+      if (kStageO && stored_slot >= 0) {
+        if (lane == 0) {
+          ptx::bulk_wait_group_read0();
+          ptx::mbar_arrive(bar(BAR_Q_STORED + stored_slot));
+        }
+        stored_slot = -1;
+      }
+    };
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      const TileInfo ti = tile_info(p, tile, nq, nk, eps);
+      const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
       const int n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps, n_plain = ti.n_plain;
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 27, 0);
+      release_staged();
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 28, 0);
       T* o_base = static_cast<T*>(p.o) + ti.b * p.os[0] + ti.h * p.os[1] +
                   static_cast<int64_t>(ti.qblk) * kTileM * p.os[2];
       uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + kOC * quarter);
@@ -581,7 +592,6 @@ attn_fwd_tc_kernel(const AttnParams p,
         continue;
       }
       float m = -INFINITY, l = 0.f;                // lines 103-104; l holds this group's partial sum
-      bool all_finite = false;                     // every row of the warp holds a finite running max
       for (int j = 0; j < n_steps; ++j) {
         const int g = g0 + j;                      // steps since the kernel started: buffer and phase
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 0, j);
@@ -597,11 +607,13 @@ attn_fwd_tc_kernel(const AttnParams p,
         for (int c = 0; c < kCW / 32; ++c) w[c] = 0xffffffffu;
         if (masked) {
           const int u = gu + (j - n_plain), st = u % kBitStages;
+          if (threadIdx.x == 128) SA_TRACE_EVENT(4, 5, j);
           ptx::mbar_wait(bar(BAR_BITS_FULL + st), (u / kBitStages) & 1, abort_flag);
+          if (threadIdx.x == 128) SA_TRACE_EVENT(4, 6, j);
 #pragma unroll
           for (int c = 0; c < kCW / 32; ++c) {
             const int ss = quarter * (kCW / 32) + c;           // sub-slot of the step
-            const int e = j * eps + ss / sps;
+            const int e = (j << eps_shift) + (ss >> sps_shift);
             w[c] = e < n_full ? 0xffffffffu : (e < total ? bits_smem[(st * 4 + ss) * 128 + row] : 0u);
           }
           ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
@@ -621,40 +633,35 @@ attn_fwd_tc_kernel(const AttnParams p,
         }
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 2, j);
 
-        // Rows that already hold a finite running max exponentiate against it straight away
-        // (one pass); the max only moves when a score exceeds it by more than the threshold.
-        if (!all_finite) all_finite = !__any_sync(0xffffffffu, m == -INFINITY);
-        const bool slow = !all_finite;
-        float m_new = m, alpha = 1.f, m_ref = m;
+        // One pass against the row's running reference max; a row that has accumulated nothing yet is
+        // tried against 0.  The reference only moves (and the pass is redone from the intact scores)
+        // when a score exceeds it by more than the threshold, or when a fresh row's largest score
+        // lies so far below 0 that P would lose precision.  A row that has seen no attended key at
+        // all keeps m = -inf and l = 0.
+        const bool fresh = m == -INFINITY;
+        const float m_try = fresh ? 0.f : m;
+        float m_new = m, alpha = 1.f;
         bool second_pass = true;
-        if (!slow) {
+        {
           float sum, xmax;
-          if (SA_DEBUG_FLAGS & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m, w, sum, xmax);
-          else if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
-          else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m, w, sum, xmax);
+          if (SA_DEBUG_FLAGS & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
+          else if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
+          else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
           *xch_mine = xmax;
           ptx::named_bar_sync(1 + lq, 32 * kSplit);
           const float xrow = row_max();
-          if (!__any_sync(0xffffffffu, xrow > kRescaleThreshold)) {
+          const bool seen = xrow > -INFINITY;
+          const bool moved = xrow > kRescaleThreshold || (fresh && seen && xrow < kFreshFloor);
+          if (!__any_sync(0xffffffffu, moved)) {
             l += sum;
+            if (seen) m = m_try;
             second_pass = false;
-          } else if (xrow > kRescaleThreshold) {
-            m_new = m + xrow;
-            alpha = ex2_approx(-xrow);                              // exp2(m - m_new), line 55
-            m_ref = m_new;
+          } else if (moved) {
+            m_new = m_try + xrow;                                   // lines 48 / 50
+            alpha = fresh ? 1.f : ex2_approx(-xrow);                // exp2(m - m_new), line 55
+          } else if (seen) {
+            m_new = m_try;
           }
-        } else {
-          float smax;
-          if (masked) max_pass<true, kCW>(tS_mine, w, smax);
-          else        max_pass<false, kCW>(tS_mine, w, smax);
-          *xch_mine = smax;
-          ptx::named_bar_sync(1 + lq, 32 * kSplit);
-          const float srow = row_max();
-          const float m_tile = srow * scale;                        // lines 48 / 50
-          const float m_cand = fmaxf(m, m_tile);
-          if (m == -INFINITY) { m_new = m_cand; }                   // nothing accumulated yet
-          else if (m_cand > m + kRescaleThreshold) { m_new = m_cand; alpha = ex2_approx(m - m_new); }
-          m_ref = (m_new == -INFINITY) ? 0.f : m_new;               // guard the reference lacks (line 53)
         }
         if (second_pass) {
           if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this thread's O columns
@@ -674,8 +681,8 @@ attn_fwd_tc_kernel(const AttnParams p,
           }
           float sum, xmax;
           static_assert(kCW / 32 <= 2, "the out-of-line pass takes two mask words");
-          softmax_pass_cold<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_ref, w[0], w[kCW / 32 - 1],
-                                                       &sum, &xmax);
+          softmax_pass_cold<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_new == -INFINITY ? 0.f : m_new,
+                                                       w[0], w[kCW / 32 - 1], &sum, &xmax);
           l = l * alpha + sum;                                      // line 57
           m = m_new;                                                // line 56
         }
@@ -687,8 +694,10 @@ attn_fwd_tc_kernel(const AttnParams p,
       }
       // ---- epilogue of the tile: O / l.  The row sums of the column groups meet in a buffer of their
       // own (the per-step exchange buffers may already be in use by the next tile's first step).
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 23, n_steps);
       ptx::mbar_wait(bar(BAR_O_FULL), tq & 1, abort_flag);
       ptx::tc_fence_after();
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 24, n_steps);
       float* xl = xch + 2 * kSplit * 128;
       xl[quarter * 128 + row] = l;
       ptx::named_bar_sync(1 + lq, 32 * kSplit);
@@ -707,8 +716,34 @@ attn_fwd_tc_kernel(const AttnParams p,
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar(BAR_O_FREE));                            // O may be overwritten by the next tile
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 25, n_steps);
       // A wait that ran out leaves the abort flag set; nothing is written in that case.
-      if (*abort_flag == 0) {
+      if constexpr (kStageO) {
+        // This warp's 32 rows x 128 bytes go to a 4 KB slab of the tile's Q slot (every MMA that read Q
+        // completed before O did) in the 128-byte swizzle, then to global memory as one TMA box.
+        const int qs = tq & 1;
+        const uint32_t slab = sQ + qs * L::kTileBytes + static_cast<uint32_t>(quarter * 4 + lq) * 4096u;
+        const bool live = *abort_flag == 0;
+#pragma unroll
+        for (int i = 0; i < kOC / 8; ++i) {
+          const uint32_t a = slab + lane * 128u + (static_cast<uint32_t>(i ^ (lane & 7)) << 4);
+          ptx::st_shared_v4(a,
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 0]) * inv, __uint_as_float(ro[8 * i + 1]) * inv),
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 2]) * inv, __uint_as_float(ro[8 * i + 3]) * inv),
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 4]) * inv, __uint_as_float(ro[8 * i + 5]) * inv),
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 6]) * inv, __uint_as_float(ro[8 * i + 7]) * inv));
+        }
+        if (threadIdx.x == 128) SA_TRACE_EVENT(4, 29, n_steps);
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (threadIdx.x == 128) SA_TRACE_EVENT(4, 30, n_steps);
+        if (lane == 0 && live) {
+          ptx::tma_store_4d(&tm_o, slab, kOC * quarter, ti.qblk * kTileM + lq * 32, p.os[1] ? ti.h : 0,
+                            p.os[0] ? ti.b : 0);                                      // line 146
+          ptx::bulk_commit_group();
+        }
+        stored_slot = qs;
+      } else if (*abort_flag == 0) {
 #pragma unroll
         for (int i = 0; i < kOC / 8; ++i) {
           uint4 v;
@@ -719,10 +754,12 @@ attn_fwd_tc_kernel(const AttnParams p,
           dst[i] = v;                                               // line 146
         }
       }
+      if (threadIdx.x == 128) SA_TRACE_EVENT(4, 26, n_steps);
       g0 += n_steps;
       gu += n_steps - n_plain;
       ++tq;
     }
+    release_staged();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -793,7 +830,7 @@ bool tma_friendly(const void* base, const int64_t* st, int S) {
 
 template <typename T, int D>
 int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                cudaStream_t stream) {
+                const CUtensorMap& mo, cudaStream_t stream) {
   auto kernel = attn_fwd_tc_kernel<T, D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(Smem<D>::dynamic_bytes));
@@ -808,7 +845,7 @@ int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& m
     sm_count = sms;
   }
   const int grid = n_tiles < sm_count ? n_tiles : sm_count;    // persistent: one CTA per SM walks the tiles
-  kernel<<<grid, kThreadsTC, Smem<D>::dynamic_bytes, stream>>>(p, mq, mk, mv, n_tiles);
+  kernel<<<grid, kThreadsTC, Smem<D>::dynamic_bytes, stream>>>(p, mq, mk, mv, mo, n_tiles);
   return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 
@@ -838,16 +875,17 @@ extern "C" int sa_debug_read_trace(long long* host, int n) {
 
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
   if (!attn_tc_supported(p)) return SA_ERR_UNSUPPORTED;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if (!make_map(&mq, p.q, p.dtype, p.B, p.H, p.Sq, p.D, p.qs, kTileM)) return SA_ERR_CUDA;
   if (!make_map(&mk, p.k, p.dtype, p.B, p.H, p.Sk, p.D, p.ks, p.BK)) return SA_ERR_CUDA;
   if (!make_map(&mv, p.v, p.dtype, p.B, p.H, p.Sk, p.D, p.vs, p.BK)) return SA_ERR_CUDA;
+  if (!make_map(&mo, p.o, p.dtype, p.B, p.H, p.Sq, p.D, p.os, 32)) return SA_ERR_CUDA;     // one softmax warp's rows
   if (p.dtype == SA_DTYPE_BF16) {
-    return p.D == 128 ? launch_inst<__nv_bfloat16, 128>(p, mq, mk, mv, stream)
-                      : launch_inst<__nv_bfloat16, 64>(p, mq, mk, mv, stream);
+    return p.D == 128 ? launch_inst<__nv_bfloat16, 128>(p, mq, mk, mv, mo, stream)
+                      : launch_inst<__nv_bfloat16, 64>(p, mq, mk, mv, mo, stream);
   }
-  return p.D == 128 ? launch_inst<__half, 128>(p, mq, mk, mv, stream)
-                    : launch_inst<__half, 64>(p, mq, mk, mv, stream);
+  return p.D == 128 ? launch_inst<__half, 128>(p, mq, mk, mv, mo, stream)
+                    : launch_inst<__half, 64>(p, mq, mk, mv, mo, stream);
 }
 
 }  // namespace sa
