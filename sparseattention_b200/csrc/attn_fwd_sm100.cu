@@ -79,8 +79,7 @@ enum Bar : int {
   BAR_PV_DONE = BAR_P_FULL + 2,                    // 2: O += P.V of step j complete (barrier j & 1)
   BAR_O_FULL = BAR_PV_DONE + 2,                    // last O += P.V of a tile complete
   BAR_O_FREE,                                      // the epilogue has read O out of tensor memory
-  BAR_BITS_FULL,                                   // kBitStages
-  BAR_BITS_EMPTY = BAR_BITS_FULL + kBitStages,
+  BAR_BITS_EMPTY,                                  // kBitStages: bit-mask tiles of a masked step read by the softmax
   BAR_Q_STORED = BAR_BITS_EMPTY + kBitStages,      // 2: the O tile staged in the Q slot has been read by its store
   BAR_COUNT = BAR_Q_STORED + 2
 };
@@ -213,20 +212,6 @@ __device__ __forceinline__ void softmax_pass(uint32_t t_s, uint32_t t_p, float s
   xmax_out = xmax;
 }
 
-// The same pass out of line, for the rare second pass after the running max moved (keeps the hot
-// loop's code small).
-template <typename T, bool kMasked, int kPolyEvery, int kCW>
-__device__ __noinline__ void softmax_pass_cold(uint32_t t_s, uint32_t t_p, float scale, float m_ref,
-                                               uint32_t w0, uint32_t w1, float* sum_out, float* xmax_out) {
-  uint32_t w[kCW / 32];
-  w[0] = w0;
-  if (kCW / 32 > 1) w[kCW / 32 - 1] = w1;
-  float sum, xmax;
-  softmax_pass<T, kMasked, kPolyEvery, kCW>(t_s, t_p, scale, m_ref, w, sum, xmax);
-  *sum_out = sum;
-  *xmax_out = xmax;
-}
-
 // Moves kCols fp32 columns between tensor memory and registers (kCols = 32 or 16).
 template <int kCols>
 __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&r)[kCols]) {
@@ -235,6 +220,37 @@ __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&r)[kCo
 template <int kCols>
 __device__ __forceinline__ void tmem_store_cols(uint32_t taddr, const uint32_t (&r)[kCols]) {
   if constexpr (kCols == 32) ptx::tmem_st32(taddr, r); else ptx::tmem_st16(taddr, r);
+}
+
+// The rare second pass of a step, after the reference max of some row moved, out of line so that the
+// hot loop stays small: rescales this thread's O columns by alpha (sparse_attn_kernel.py:58) when
+// asked to, then redoes the pass from the intact scores against m_ref.  Returns the new row sum.
+template <typename T, int kCW, int kOC>
+__device__ __noinline__ float second_pass_cold(uint32_t t_s, uint32_t t_p, uint32_t t_o, float scale, float m_ref,
+                                               float alpha, bool rescale_o, uint32_t pv_bar, uint32_t pv_parity,
+                                               volatile int* abort_flag, uint32_t w0, uint32_t w1) {
+  constexpr int kOChunk = kOC > 32 ? 32 : kOC;
+  if (rescale_o) {
+    // O must hold every product up to the previous step before it is rescaled.
+    ptx::mbar_wait(pv_bar, pv_parity, abort_flag);
+    ptx::tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < kOC / kOChunk; ++c) {
+      uint32_t r[kOChunk];
+      tmem_load_cols<kOChunk>(t_o + c * kOChunk, r);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < kOChunk; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+      tmem_store_cols<kOChunk>(t_o + c * kOChunk, r);
+    }
+  }
+  static_assert(kCW / 32 <= 2, "the out-of-line pass takes two mask words");
+  uint32_t w[kCW / 32];
+  w[0] = w0;
+  if (kCW / 32 > 1) w[kCW / 32 - 1] = w1;
+  float sum, xmax;
+  softmax_pass<T, true, kPolyMasked, kCW>(t_s, t_p, scale, m_ref, w, sum, xmax);
+  return sum;
 }
 
 // Work of one (query block, batch, head) tile, read from the lists.
@@ -307,7 +323,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       ptx::mbar_init(bar(BAR_Q_FULL + i), 1);
       ptx::mbar_init(bar(BAR_Q_EMPTY + i), 1);
       ptx::mbar_init(bar(BAR_S_FULL + i), 1);
-      ptx::mbar_init(bar(BAR_P_FULL + i), 128 * kSplit);
+      ptx::mbar_init(bar(BAR_P_FULL + i), 4 * kSplit);      // one arrival per softmax warp
       ptx::mbar_init(bar(BAR_PV_DONE + i), 1);
       ptx::mbar_init(bar(BAR_Q_STORED + i), 4 * kSplit);
     }
@@ -320,10 +336,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       ptx::mbar_init(bar(BAR_V_EMPTY + i), 1);
     }
     ptx::mbar_init(bar(BAR_O_FULL), 1);
-    ptx::mbar_init(bar(BAR_O_FREE), 128 * kSplit);
+    ptx::mbar_init(bar(BAR_O_FREE), 4 * kSplit);
     for (int i = 0; i < kBitStages; ++i) {
-      ptx::mbar_init(bar(BAR_BITS_FULL + i), 1);
-      ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 128 * kSplit);
+      ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 4 * kSplit);
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -407,9 +422,23 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         if (lane == 0) SA_TRACE_EVENT(warp, 0, j);
         const uint32_t dst = s_tiles + st * L::kTileBytes;
         const uint32_t full_bar = bar(bar_full + st);
+        // The bit-mask tiles of the partial blocks of step j land on the K tile's barrier: once
+        // S(j) is complete the softmax finds them in shared memory without a wait of its own.
+        const bool with_bits = is_k && j >= n_plain;
+        const int u = gu + (j - n_plain), bst = u % kBitStages;
+        uint32_t tx_bytes = (SA_DEBUG_FLAGS & 2) ? slot_bytes : L::kTileBytes;
+        if (with_bits) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int e = (j << eps_shift) + (c >> sps_shift);
+            tx_bytes += (e >= n_full && e < total) ? 512u : 0u;
+          }
+        }
         if (lane == 0) {
           if (round > 0) ok = ptx::mbar_wait(bar(bar_empty + st), (round - 1) & 1, abort_flag);
-          if (ok) ptx::mbar_arrive_expect_tx(full_bar, (SA_DEBUG_FLAGS & 2) ? slot_bytes : L::kTileBytes);
+          if (ok && with_bits && u >= kBitStages)
+            ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
+          if (ok) ptx::mbar_arrive_expect_tx(full_bar, tx_bytes);
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (lane == 0) SA_TRACE_EVENT(warp, 1, j);
@@ -418,29 +447,14 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
           ptx::tma_load_4d(dst + pnl_of_lane * kPanelBytes + c_of_lane * slot_bytes, tm, full_bar,
                            pnl_of_lane * 64, id_c * p.BK, ch, cb);
         if (lane == 0) SA_TRACE_EVENT(warp, 2, j);
-        if (is_k && j >= n_plain && ok) {               // bit-mask tiles of the partial blocks of step j
-          const int u = gu + (j - n_plain), bst = u % kBitStages;
-          int n_bit_tiles = 0;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int e = (j << eps_shift) + (c >> sps_shift);
-            n_bit_tiles += (e >= n_full && e < total) ? 1 : 0;
-          }
-          if (lane == 0) {
-            if (u >= kBitStages) ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
-            if (ok) {
-              if (n_bit_tiles > 0) ptx::mbar_arrive_expect_tx(bar(BAR_BITS_FULL + bst), 512u * n_bit_tiles);
-              else ptx::mbar_arrive(bar(BAR_BITS_FULL + bst));
-            }
-          }
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (with_bits) {
           const int c = lane & 3, ec = c >> sps_shift;
           const int id_b = __shfl_sync(0xffffffffu, id_cur, ec);
           const int e = (j << eps_shift) + ec;
           if (ok && lane < 4 && e >= n_full && e < total) {
             const int64_t kb32 = (static_cast<int64_t>(id_b) << sps_shift) + (c & ((1 << sps_shift) - 1));
             const uint32_t* src = bits_plane + kb32 * p.Sq + qblk * kTileM;
-            ptx::bulk_load(sBits + static_cast<uint32_t>(bst * 4 + c) * 512u, src, 512u, bar(BAR_BITS_FULL + bst));
+            ptx::bulk_load(sBits + static_cast<uint32_t>(bst * 4 + c) * 512u, src, 512u, full_bar);
           }
         }
         id_cur = id_nxt; id_nxt = id_nxt2;
@@ -469,10 +483,10 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         const uint32_t dq_lo = dq_lo0 + qs * (L::kTileBytes >> 4);
         for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
           SA_TRACE_EVENT(2, 0, j);
-          // Buffer g & 1 is reused: its scores were read by the softmax of step g-2 and its P by
-          // O += P.V of step g-2.  The latter implies the former, and having it complete before S(g)
-          // lets the softmax of step g write P without a wait of its own.
-          if (g >= 2) ok = ptx::mbar_wait(bar(BAR_PV_DONE + (g & 1)), ((g - 2) >> 1) & 1, abort_flag);
+          // Score buffer g & 1 is reused: the softmax of step g-2 has read it once P(g-2) is complete.
+          // (The P buffer of the same parity is still being read by O += P.V(g-2); the softmax of
+          // step g waits for that product itself before it writes P.)
+          if (g >= 2) ok = ptx::mbar_wait(bar(BAR_P_FULL + (g & 1)), ((g - 2) >> 1) & 1, abort_flag);
           if (!ok) break;
           SA_TRACE_EVENT(2, 1, j);
           ok = ptx::mbar_wait(bar(BAR_K_FULL + st), round & 1, abort_flag);
@@ -596,6 +610,8 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         const int g = g0 + j;                      // steps since the kernel started: buffer and phase
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 0, j);
         ptx::mbar_wait(bar(BAR_S_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
+        // P buffer g & 1 is written below: O += P.V(g-2), which read it, must be complete.
+        if (g >= 2) ptx::mbar_wait(bar(BAR_PV_DONE + (g & 1)), ((g - 2) >> 1) & 1, abort_flag);
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 1, j);
         ptx::tc_fence_after();
         // this group's scores of buffer g & 1, and where its P goes
@@ -607,16 +623,15 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         for (int c = 0; c < kCW / 32; ++c) w[c] = 0xffffffffu;
         if (masked) {
           const int u = gu + (j - n_plain), st = u % kBitStages;
-          if (threadIdx.x == 128) SA_TRACE_EVENT(4, 5, j);
-          ptx::mbar_wait(bar(BAR_BITS_FULL + st), (u / kBitStages) & 1, abort_flag);
-          if (threadIdx.x == 128) SA_TRACE_EVENT(4, 6, j);
 #pragma unroll
           for (int c = 0; c < kCW / 32; ++c) {
             const int ss = quarter * (kCW / 32) + c;           // sub-slot of the step
             const int e = (j << eps_shift) + (ss >> sps_shift);
-            w[c] = e < n_full ? 0xffffffffu : (e < total ? bits_smem[(st * 4 + ss) * 128 + row] : 0u);
+            const uint32_t word = bits_smem[(st * 4 + ss) * 128 + row];    // stale for a full or padding slot
+            w[c] = e < n_full ? 0xffffffffu : (e < total ? word : 0u);
           }
-          ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
         }
         float* xch_mine = xch + ((g & 1) * kSplit + quarter) * 128 + row;
         const float* xch_row = xch + (g & 1) * kSplit * 128 + row;
@@ -628,7 +643,8 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         };
         if (SA_DEBUG_FLAGS & 1) {
           ptx::tc_fence_before();
-          ptx::mbar_arrive(bar(BAR_P_FULL + (g & 1)));
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar(BAR_P_FULL + (g & 1)));
           continue;
         }
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 2, j);
@@ -664,32 +680,20 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
           }
         }
         if (second_pass) {
-          if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {     // acc *= alpha (line 58), this thread's O columns
-            // O must hold every product up to step g-1 before it is rescaled.  P.V(g-2) completed
-            // before S(g) was issued, so this barrier is at most one phase behind.
-            ptx::mbar_wait(bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag);
-            ptx::tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < kOC / kOChunk; ++c) {
-              uint32_t r[kOChunk];
-              tmem_load_cols<kOChunk>(tO_mine + c * kOChunk, r);
-              ptx::tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < kOChunk; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_store_cols<kOChunk>(tO_mine + c * kOChunk, r);
-            }
-          }
-          float sum, xmax;
-          static_assert(kCW / 32 <= 2, "the out-of-line pass takes two mask words");
-          softmax_pass_cold<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_new == -INFINITY ? 0.f : m_new,
-                                                       w[0], w[kCW / 32 - 1], &sum, &xmax);
+          // This step waited for P.V(g-2) and the previous one for P.V(g-3): the barrier of step g-1 is at
+          // most one phase behind.
+          const bool rescale_o = j > 0 && __any_sync(0xffffffffu, alpha != 1.f);
+          const float sum = second_pass_cold<T, kCW, kOC>(
+              tS_mine, tP_mine, tO_mine, scale, m_new == -INFINITY ? 0.f : m_new, alpha, rescale_o,
+              bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag, w[0], w[kCW / 32 - 1]);
           l = l * alpha + sum;                                      // line 57
           m = m_new;                                                // line 56
         }
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 3, j);
         ptx::tmem_st_wait();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(bar(BAR_P_FULL + (g & 1)));
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(BAR_P_FULL + (g & 1)));    // one arrival per softmax warp
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 4, j);
       }
       // ---- epilogue of the tile: O / l.  The row sums of the column groups meet in a buffer of their
@@ -715,7 +719,8 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         for (int i = 0; i < kOChunk; ++i) ro[c * kOChunk + i] = r[i];
       }
       ptx::tc_fence_before();
-      ptx::mbar_arrive(bar(BAR_O_FREE));                            // O may be overwritten by the next tile
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar(BAR_O_FREE));             // O may be overwritten by the next tile
       if (threadIdx.x == 128) SA_TRACE_EVENT(4, 25, n_steps);
       // A wait that ran out leaves the abort flag set; nothing is written in that case.
       if constexpr (kStageO) {
