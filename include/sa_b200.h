@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define SA_ABI_VERSION 1
+#define SA_ABI_VERSION 2
 
 /* status codes */
 #define SA_OK                     0
@@ -101,6 +101,10 @@ int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int
                          const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                          int has_packed_bits);
 
+/* Bytes of scratch sa_attn_fwd can use (a counter from which the CTAs of the tcgen05 kernel draw their
+ * (query block, batch, head) tiles, so that uneven lists do not leave SMs idle at the end). */
+size_t sa_attn_workspace_bytes(void);
+
 /* Stage 2: block-sparse attention forward.  Replaces sparse_attention /
  * sparse_attention_kernel / _sparse_inner (sparseattention/sparse_attn_kernel.py:149-185,
  * 72-146, 10-63): per query block, a mask-free loop over the full list, then a masked
@@ -115,6 +119,9 @@ int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int
  *   3 element strides (b,h,q).  Only ids[..., :len] is read; they are trusted like the
  *   reference trusts a caller-supplied MaskMetadata (sparse_attn_kernel.py:157-163).
  * scale_log2: softmax scale already multiplied by log2(e) (sparse_attn_kernel.py:152).
+ * workspace: optional sa_attn_workspace_bytes() bytes of device memory, 4-byte aligned; the call clears
+ *   it on the stream.  NULL (or too small): the tiles are dealt to the CTAs in a fixed round-robin order.
+ *   Calls that may overlap on the GPU need a workspace each.
  * dev_status: optional device int32, set non-zero by the kernel on a device-side problem. */
 int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int64_t* q_strides, const int64_t* k_strides,
@@ -126,7 +133,8 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int32_t* full_lens, const int64_t* full_lens_strides,
                 const int32_t* part_ids, const int64_t* part_ids_strides,
                 const int32_t* part_lens, const int64_t* part_lens_strides,
-                float scale_log2, int impl, int32_t* dev_status, void* stream);
+                float scale_log2, int impl, void* workspace, size_t workspace_bytes,
+                int32_t* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -17,7 +17,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("SPARSEATTN_B200_LIB") or os.path.join(_PKG_DIR, "libsparseattn_b200.so")
 
 # mirrors of the header's constants
-SA_ABI_VERSION = 1
+SA_ABI_VERSION = 2
 SA_OK = 0
 SA_DTYPE_F32, SA_DTYPE_F16, SA_DTYPE_BF16 = 0, 1, 2
 SA_IMPL_AUTO, SA_IMPL_SIMT, SA_IMPL_TCGEN05 = 0, 1, 2
@@ -41,7 +41,8 @@ SYMBOLS = {
                          _i, _i, _i, _i, _i, _i, _i, _i,
                          _p, _p, _p, _i64, _i64,
                          _p, _p, _p, _p, _p, _p, _p, _p,
-                         _f, _i, _p, _p]),
+                         _f, _i, _p, _sz, _p, _p]),
+    "sa_attn_workspace_bytes": (_sz, []),
 }
 
 _lib = None
@@ -214,6 +215,8 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
         else:
             bsb = bsh = 0
         status = torch.zeros((1,), dtype=torch.int32, device=dev) if check_status else None
+        ws_bytes = int(lib.sa_attn_workspace_bytes())
+        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)        # cleared by the call
         rc = lib.sa_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                              _strides(q), _strides(k), _strides(v), _strides(o),
                              _DTYPES[q.dtype], B, H, Sq, Sk, D, block_q, block_k,
@@ -221,7 +224,8 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
                              bits.data_ptr() if has_bits else None, bsb, bsh,
                              full_ids.data_ptr(), _strides(full_ids), full_lens.data_ptr(), _strides(full_lens),
                              part_ids.data_ptr(), _strides(part_ids), part_lens.data_ptr(), _strides(part_lens),
-                             scale_log2, impl, status.data_ptr() if check_status else None, _stream_ptr(dev))
+                             scale_log2, impl, ws.data_ptr(), ws_bytes,
+                             status.data_ptr() if check_status else None, _stream_ptr(dev))
     _check(rc, "sa_attn_fwd")
     if check_status:
         code = int(status.item())

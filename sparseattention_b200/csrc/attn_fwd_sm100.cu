@@ -3,9 +3,9 @@
 // Replaces sparseattention/sparse_attn_kernel.py:72-146 (kernel) and 10-63 (inner loop)
 // for fp16 / bf16, head dim 64 or 128, BLOCK_Q = 128 and BLOCK_K in {32, 64, 128}.
 //
-// Persistent grid: one CTA per SM (384 threads) walks the (query block, batch, head) tiles
-// blockIdx.x, blockIdx.x + gridDim.x, ...; the loads and first MMAs of a tile overlap the epilogue
-// of the previous one (Q is double-buffered, barrier phases run on across tiles).  For a tile --
+// Persistent grid: one CTA per SM (384 threads) works through (query block, batch, head) tiles drawn
+// from a device-wide counter (tiles differ in length); the loads and first MMAs of a tile overlap the
+// epilogue of the previous one (Q is double-buffered, barrier phases run on across tiles).  For a tile --
 // one query block (128 rows) of one (batch, head) -- the CTA walks its two kv-block lists -- the full list first, then the partial list: the order of
 // sparse_attn_kernel.py:113-142 -- in steps of 128 kv rows (128 / BLOCK_K listed blocks):
 //
@@ -55,9 +55,13 @@ constexpr uint32_t kTmemCols = 512;  // score buffers at columns 0 and 128, O at
 constexpr int kStagesK = 2;          // K tiles in flight in shared memory
 constexpr int kStagesV = 2;          // V tiles in flight in shared memory
 constexpr int kBitStages = 4;        // steps of bit-mask tiles in flight
+constexpr int kTileRing = 4;         // tile indices the scheduling warp may be ahead of the slowest role
 constexpr uint32_t kPanelBytes = 128u * 128u;   // 128 rows x 64 elements x 2 B
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 constexpr float kFreshFloor = -4.0f;            // a row's first scores are taken against 0 if their max is in [-4, 8]
+#ifndef SA_SOFTMAX_ACC
+#define SA_SOFTMAX_ACC 2
+#endif
 #ifndef SA_POLY_PLAIN
 #define SA_POLY_PLAIN 0
 #endif
@@ -81,7 +85,9 @@ enum Bar : int {
   BAR_O_FREE,                                      // the epilogue has read O out of tensor memory
   BAR_BITS_EMPTY,                                  // kBitStages: bit-mask tiles of a masked step read by the softmax
   BAR_Q_STORED = BAR_BITS_EMPTY + kBitStages,      // 2: the O tile staged in the Q slot has been read by its store
-  BAR_COUNT = BAR_Q_STORED + 2
+  BAR_TILE_FULL = BAR_Q_STORED + 2,                // kTileRing: a tile index has been published
+  BAR_TILE_EMPTY = BAR_TILE_FULL + kTileRing,      // kTileRing: every other role has read it
+  BAR_COUNT = BAR_TILE_EMPTY + kTileRing
 };
 
 template <int D>
@@ -92,8 +98,8 @@ struct Smem {
   static constexpr uint32_t off_v = off_k + kStagesK * kTileBytes;
   static constexpr uint32_t off_bits = off_v + kStagesV * kTileBytes;      // [kBitStages][4 sub-slots][128 rows] u32
   static constexpr uint32_t off_bar = off_bits + kBitStages * 4 * 128 * 4;
-  static constexpr uint32_t off_misc = off_bar + 8 * 32;
-  static constexpr uint32_t off_xch = off_misc + 16;             // [2 parities + epilogue][kSplit column groups][128 rows] f32
+  static constexpr uint32_t off_misc = off_bar + 8 * 48;
+  static constexpr uint32_t off_xch = off_misc + 16 + 4 * kTileRing;   // misc: TMEM base, abort flag, tile ring             // [2 parities + epilogue][kSplit column groups][128 rows] f32
   static constexpr uint32_t total = off_xch + 3 * kSplit * 128 * 4;
 #ifdef SA_TRACE
   static constexpr uint32_t dynamic_bytes = total + 1024 + 5 * 500 * 8;
@@ -101,7 +107,7 @@ struct Smem {
   static constexpr uint32_t dynamic_bytes = total + 1024;       // slack to align the base to 1024 B
 #endif
 };
-static_assert(BAR_COUNT <= 32, "barrier area too small");
+static_assert(BAR_COUNT <= 48, "barrier area too small");
 
 template <typename T> struct Fmt;
 template <> struct Fmt<__half> {
@@ -152,11 +158,16 @@ __device__ __forceinline__ float ex2_approx(float x) {
 
 // 32 score columns of one thread: x = s*scale - m_ref, masked columns -> -inf (kMasked), P = exp2(x)
 // rounded to T into pk, fp32 sum of the unrounded P (lines 54, 57, 61) and max of x.
+// The running max and sum are kept in kAcc independent accumulators each (pair i goes to i % kAcc), so
+// that consecutive pairs do not wait for one another's result.
+constexpr int kAcc = SA_SOFTMAX_ACC;
 template <typename T, bool kMasked, int kPolyEvery, bool kNoExp>
 __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t w, uint64_t scale2, uint64_t nm2,
-                                              uint32_t (&pk)[16], uint64_t& sum2, float& xmax) {
+                                              uint32_t (&pk)[16], uint64_t (&sum2v)[kAcc], float (&xmaxv)[kAcc]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
+    uint64_t& sum2 = sum2v[i % kAcc];
+    float& xmax = xmaxv[i % kAcc];
     float x0, x1;
     ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_u32x2(r[2 * i], r[2 * i + 1]), scale2, nm2), x0, x1);
     if (kMasked) {
@@ -177,39 +188,50 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t 
 // One pass over this thread's kCW score columns, kCW / 32 chunks of 32.  w[c] is the bit-mask word
 // of chunk c for this thread's row; a warp covers 32 rows, so on masked steps a chunk is one 32 x 32
 // block of the mask.  A block that is False for all 32 rows costs no arithmetic (P = 0, no
-// exponentials).  (A third, mask-free variant for all-True blocks made the loop body large enough
-// to lose more than it won.)
-template <typename T, bool kMasked, int kPolyEvery, int kCW, bool kNoExp = false>
+// exponentials); one that is True for all 32 rows takes the mask-free arithmetic.
+struct NoTrace { __device__ __forceinline__ void operator()(int) const {} };
+template <typename T, bool kMasked, int kPolyEvery, int kCW, bool kNoExp = false, typename Tr = NoTrace>
 __device__ __forceinline__ void softmax_pass(uint32_t t_s, uint32_t t_p, float scale, float m_ref,
-                                             const uint32_t (&w)[kCW / 32], float& sum_out, float& xmax_out) {
+                                             const uint32_t (&w)[kCW / 32], float& sum_out, float& xmax_out,
+                                             Tr&& tr = Tr()) {
   constexpr int kChunks = kCW / 32;
-  bool dead[kChunks];
+  bool dead[kChunks], solid[kChunks];
   uint32_t r[kChunks][32];
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     dead[c] = kMasked && __all_sync(0xffffffffu, w[c] == 0u);
+    solid[c] = !kMasked || __all_sync(0xffffffffu, w[c] == 0xffffffffu);
     ptx::tmem_ld32(t_s + 32 * c, r[c]);
   }
+  tr(50);
   ptx::tmem_ld_wait();
+  tr(51);
   const uint64_t scale2 = ptx::pack_f32x2(scale, scale);
   const uint64_t nm2 = ptx::pack_f32x2(-m_ref, -m_ref);
-  uint64_t sum2 = ptx::pack_f32x2(0.f, 0.f);
-  float xmax = -INFINITY;
+  uint64_t sum2[kAcc];
+  float xmax[kAcc];
+#pragma unroll
+  for (int a = 0; a < kAcc; ++a) { sum2[a] = ptx::pack_f32x2(0.f, 0.f); xmax[a] = -INFINITY; }
 #pragma unroll
   for (int c = 0; c < kChunks; ++c) {
     uint32_t pk[16];
     if (dead[c]) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) pk[i] = 0u;
+    } else if (solid[c]) {
+      softmax_chunk<T, false, kPolyEvery, kNoExp>(r[c], w[c], scale2, nm2, pk, sum2, xmax);
     } else {
-      softmax_chunk<T, kMasked, kPolyEvery, kNoExp>(r[c], w[c], scale2, nm2, pk, sum2, xmax);
+      softmax_chunk<T, true, kPolyEvery, kNoExp>(r[c], w[c], scale2, nm2, pk, sum2, xmax);
     }
     ptx::tmem_st16(t_p + 16 * c, pk);
+    tr(52 + c);
   }
+#pragma unroll
+  for (int a = 1; a < kAcc; ++a) { sum2[0] = ptx::add_f32x2(sum2[0], sum2[a]); xmax[0] = fmaxf(xmax[0], xmax[a]); }
   float s0, s1;
-  ptx::unpack_f32x2(sum2, s0, s1);
+  ptx::unpack_f32x2(sum2[0], s0, s1);
   sum_out = s0 + s1;
-  xmax_out = xmax;
+  xmax_out = xmax[0];
 }
 
 // Moves kCols fp32 columns between tensor memory and registers (kCols = 32 or 16).
@@ -294,6 +316,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
   auto bar = [&](int i) { return sbase + L::off_bar + 8u * static_cast<uint32_t>(i); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
+  volatile int* tile_ring = reinterpret_cast<volatile int*>(smem + L::off_misc + 16);
   float* xch = reinterpret_cast<float*>(smem + L::off_xch);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -340,6 +363,10 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
     for (int i = 0; i < kBitStages; ++i) {
       ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 4 * kSplit);
     }
+    for (int i = 0; i < kTileRing; ++i) {
+      ptx::mbar_init(bar(BAR_TILE_FULL + i), 1);
+      ptx::mbar_init(bar(BAR_TILE_EMPTY + i), 3 + 4 * kSplit);    // V producer, two issuers, softmax warps
+    }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
@@ -354,10 +381,29 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tO = tmem_base + 256;   // score buffer s lives at tmem_base + 128 * s, P buffer s at 384 + 64 * s
 
-  // Every role walks the same sequence of tiles (blockIdx.x, + gridDim.x, ...) and keeps the same
-  // running counts -- steps done (g), masked steps done (gu), non-empty tiles done (tq) -- from which
-  // buffer indices and barrier phases follow; nothing is reset between tiles, so the loads and the
-  // first MMAs of a tile overlap the epilogue of the previous one.
+  // Every role walks the same sequence of tiles and keeps the same running counts -- steps done (g),
+  // masked steps done (gu), non-empty tiles done (tq) -- from which buffer indices and barrier
+  // phases follow; nothing is reset between tiles, so the loads and the first MMAs of a tile overlap
+  // the epilogue of the previous one.  The sequence starts at blockIdx.x; warp 0 draws each further
+  // tile from a device-wide counter (or, without one, steps by gridDim.x) and publishes it to the
+  // other roles through a small ring in shared memory; an index >= n_tiles ends every role's loop.
+  // Ordinal `ord` of the sequence lives in ring slot ord % kTileRing.
+  auto read_tile = [&](int ord) -> int {            // one thread of a role that is not the scheduler
+    const int slot = ord % kTileRing;
+    if (!ptx::mbar_wait(bar(BAR_TILE_FULL + slot), (ord / kTileRing) & 1, abort_flag)) return n_tiles;
+    return tile_ring[slot];
+  };
+  auto next_tile_warp = [&](int ord) -> int {       // a whole warp; lane 0 hands the slot back
+    const int t = read_tile(ord);
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(bar(BAR_TILE_EMPTY + ord % kTileRing));
+    return t;
+  };
+  auto next_tile_thread = [&](int ord) -> int {     // a role run by a single thread
+    const int t = read_tile(ord);
+    ptx::mbar_arrive(bar(BAR_TILE_EMPTY + ord % kTileRing));
+    return t;
+  };
   if (warp < 2) {
     // ------------------------------------------------------------------ producers
     // Warp 0 gathers Q, the K tiles and the bit-mask tiles, warp 1 the V tiles.  The whole warp
@@ -378,11 +424,27 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
     bool bad_index = false;
     bool ok = true;
     int st = 0, round = 0, gu = 0, tq = 0;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    // lane 0 of warp 0 publishes tile `t` as ordinal `ord` of the sequence
+    auto publish = [&](int ord, int t) {
+      const int slot = ord % kTileRing;
+      if (ord >= kTileRing) ok = ptx::mbar_wait(bar(BAR_TILE_EMPTY + slot), (ord / kTileRing - 1) & 1, abort_flag);
+      tile_ring[slot] = t;
+      ptx::mbar_arrive(bar(BAR_TILE_FULL + slot));
+    };
+    int ord = 0;
+    int tile = blockIdx.x;
+    if (is_k) { if (lane == 0) publish(0, tile); } else { tile = next_tile_warp(0); }
+    while (tile < n_tiles && ok) {
+      // The next tile is drawn now and published after this one's loads are issued: the answer of
+      // the atomic is not waited for until then.
+      int drawn = 0;
+      if (is_k && lane == 0)
+        drawn = p.tile_counter != nullptr ? atomicAdd(p.tile_counter, 1) + static_cast<int>(gridDim.x)
+                                          : tile + static_cast<int>(gridDim.x);
       const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
-      if (ti.total == 0) continue;
       const int b = ti.b, h = ti.h, qblk = ti.qblk, n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps,
                 n_plain = ti.n_plain;
+      if (total != 0) {
       if (is_k) {                                   // Q tile of this query block, double-buffered
         const int qs = tq & 1;
         if (lane == 0) {
@@ -462,6 +524,18 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       }
       gu += n_steps - n_plain;
       ++tq;
+      }
+      ++ord;
+      if (is_k) {
+        if (lane == 0) {
+          if (drawn < 0 || drawn > n_tiles) drawn = n_tiles;
+          publish(ord, drawn);
+        }
+        tile = __shfl_sync(0xffffffffu, drawn, 0);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      } else {
+        tile = next_tile_warp(ord);
+      }
     }
     if (is_k && __any_sync(0xffffffffu, bad_index) && lane == 0 && p.dev_status != nullptr)
       atomicMax(p.dev_status, SA_DEV_BAD_INDEX);
@@ -475,7 +549,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       const uint32_t dk_lo0 = static_cast<uint32_t>(ptx::umma_desc_sw128(sK, 16u));
       bool ok = true;
       int st = 0, round = 0, g = 0, tq = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int ord = 0; ok; ++ord) {
+        const int tile = next_tile_thread(ord);
+        if (tile >= n_tiles) break;
         const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
         if (ti.total == 0) continue;
         const int qs = tq & 1;
@@ -522,7 +598,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       const uint32_t dv_lo0 = static_cast<uint32_t>(dv), dv_hi = static_cast<uint32_t>(dv >> 32);
       bool ok = true;
       int g = 0, tq = 0;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      for (int ord = 0; ok; ++ord) {
+        const int tile = next_tile_thread(ord);
+        if (tile >= n_tiles) break;
         const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
         if (ti.total == 0) continue;
         for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
@@ -591,7 +669,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         stored_slot = -1;
       }
     };
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    for (int ord = 0;; ++ord) {
+      const int tile = next_tile_warp(ord);
+      if (tile >= n_tiles) break;
       const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
       const int n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps, n_plain = ti.n_plain;
       if (threadIdx.x == 128) SA_TRACE_EVENT(4, 27, 0);
@@ -609,9 +689,16 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       for (int j = 0; j < n_steps; ++j) {
         const int g = g0 + j;                      // steps since the kernel started: buffer and phase
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 0, j);
-        ptx::mbar_wait(bar(BAR_S_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
-        // P buffer g & 1 is written below: O += P.V(g-2), which read it, must be complete.
-        if (g >= 2) ptx::mbar_wait(bar(BAR_PV_DONE + (g & 1)), ((g - 2) >> 1) & 1, abort_flag);
+        {
+          // S(g) must be complete, and so must O += P.V(g-2), which read the P buffer written below
+          // (a barrier that has completed no phase yet passes a wait for parity 1).  Both are asked
+          // before either answer is used.
+          const uint32_t b_s = bar(BAR_S_FULL + (g & 1)), b_pv = bar(BAR_PV_DONE + (g & 1));
+          const uint32_t par_s = (g >> 1) & 1, par_pv = ((g - 2) >> 1) & 1;
+          const bool ok_s = ptx::mbar_try_wait(b_s, par_s), ok_pv = ptx::mbar_try_wait(b_pv, par_pv);
+          if (!ok_s) ptx::mbar_wait_slow(b_s, par_s, abort_flag);
+          if (!ok_pv) ptx::mbar_wait_slow(b_pv, par_pv, abort_flag);
+        }
         if (threadIdx.x == 128) SA_TRACE_EVENT(4, 1, j);
         ptx::tc_fence_after();
         // this group's scores of buffer g & 1, and where its P goes
@@ -660,9 +747,14 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         bool second_pass = true;
         {
           float sum, xmax;
-          if (SA_DEBUG_FLAGS & 8) softmax_pass<T, true, 0, kCW, true>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
-          else if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
+#ifdef SA_TRACE
+          auto tr = [&](int ev) { if (threadIdx.x == 128) SA_TRACE_EVENT(4, ev, j); };
+          if (masked) softmax_pass<T, true, kPolyMasked, kCW, false>(tS_mine, tP_mine, scale, m_try, w, sum, xmax, tr);
+          else        softmax_pass<T, false, kPolyPlain, kCW, false>(tS_mine, tP_mine, scale, m_try, w, sum, xmax, tr);
+#else
+          if (masked) softmax_pass<T, true, kPolyMasked, kCW>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
           else        softmax_pass<T, false, kPolyPlain, kCW>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
+#endif
           *xch_mine = xmax;
           ptx::named_bar_sync(1 + lq, 32 * kSplit);
           const float xrow = row_max();
@@ -850,7 +942,15 @@ int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& m
     sm_count = sms;
   }
   const int grid = n_tiles < sm_count ? n_tiles : sm_count;    // persistent: one CTA per SM walks the tiles
+#ifdef SA_STATIC_TILES
+  AttnParams pp = p;
+  pp.tile_counter = nullptr;
+  kernel<<<grid, kThreadsTC, Smem<D>::dynamic_bytes, stream>>>(pp, mq, mk, mv, mo, n_tiles);
+#else
+  if (p.tile_counter != nullptr && cudaMemsetAsync(p.tile_counter, 0, sizeof(int32_t), stream) != cudaSuccess)
+    return SA_ERR_CUDA;
   kernel<<<grid, kThreadsTC, Smem<D>::dynamic_bytes, stream>>>(p, mq, mk, mv, mo, n_tiles);
+#endif
   return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 

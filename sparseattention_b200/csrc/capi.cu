@@ -114,6 +114,8 @@ int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int
   return sa::attn_tc_supported(p);
 }
 
+size_t sa_attn_workspace_bytes(void) { return 16; }
+
 int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int64_t* q_strides, const int64_t* k_strides,
                 const int64_t* v_strides, const int64_t* o_strides,
@@ -124,7 +126,8 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int32_t* full_lens, const int64_t* full_lens_strides,
                 const int32_t* part_ids, const int64_t* part_ids_strides,
                 const int32_t* part_lens, const int64_t* part_lens_strides,
-                float scale_log2, int impl, int32_t* dev_status, void* stream) {
+                float scale_log2, int impl, void* workspace, size_t workspace_bytes,
+                int32_t* dev_status, void* stream) {
   sa::AttnParams p;
   if (o == nullptr || o_strides == nullptr) return SA_ERR_INVALID_ARGUMENT;
   int rc = fill_attn_params(p, q, k, v, o, q_strides, k_strides, v_strides, o_strides, dtype, B, H, Sq, Sk, D,
@@ -144,6 +147,10 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   p.part_lens = part_lens; copy_n(p.pls, part_lens_strides, 3);
   p.scale_log2 = scale_log2;
   p.dev_status = dev_status;
+  p.tile_counter = nullptr;
+  if (workspace != nullptr && workspace_bytes >= sa_attn_workspace_bytes() &&
+      reinterpret_cast<uintptr_t>(workspace) % 4 == 0)
+    p.tile_counter = static_cast<int32_t*>(workspace);
 #ifdef SA_TRACE
   { const char* e = getenv("SA_TC_DEBUG"); p.debug = e ? atoi(e) : 0; }
 #endif

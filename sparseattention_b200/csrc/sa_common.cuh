@@ -41,6 +41,7 @@ struct AttnParams {
   int dtype;
   float scale_log2;
   int32_t* dev_status;
+  int32_t* tile_counter;                         // zeroed device word for the tile scheduler, or null (static order)
   int debug;
 };
 

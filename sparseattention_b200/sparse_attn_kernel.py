@@ -26,9 +26,10 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     not given), exactly the call of sparse_attn_kernel.py:149.
 
     q: ``[B,H,Sq,D]``; k, v: ``[B,H,Sk,D]``; mask: bool, broadcastable to ``[B,H,Sq,Sk]``.
-    fp16 / bf16 with D in {64,128}, BLOCK_Q = 128 and BLOCK_K in {32,64,128} run the
-    TMA + tcgen05 kernel; every other combination of fp32 / fp16 / bf16, D in {16,32,64,128}
-    and block sizes that are multiples of 32 runs the generic CUDA-core kernel.  ``impl``
+    fp16 / bf16 with D in {64,128}, BLOCK_Q = 128 (or 32 / 64 when the lists are built here rather
+    than supplied) and BLOCK_K in {32,64,128} run the TMA + tcgen05 kernel; every other
+    combination of fp32 / fp16 / bf16, D in {16,32,64,128} and block sizes that are multiples of
+    32 runs the generic CUDA-core kernel.  ``impl``
     ("auto" | "tcgen05" | "simt") forces one of them.  Rows whose mask is all False return 0.
 
     ``check_status`` (default: the SPARSEATTN_B200_CHECK environment variable) makes the call
@@ -41,12 +42,19 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     if check_status is None:
         check_status = os.environ.get("SPARSEATTN_B200_CHECK", "0") not in ("", "0")
 
+    q, k, v = _native._tma_ready(q), _native._tma_ready(k), _native._tma_ready(v)
+    impl_id = _native.IMPLS[impl]
     md = mask_metadata
+    if md is None and int(BLOCK_Q) in (32, 64) and impl_id != _native.SA_IMPL_SIMT and \
+            _native.uses_tcgen05(q, k, v, 128, int(BLOCK_K), True):
+        # The tensor-core kernel works on 128 query rows at a time.  With no lists from the caller
+        # the classification is done at that height: a 128-row tile is computed when any of its
+        # BLOCK_Q-row blocks would be, and the bit plane masks the elements, so the result is the
+        # one the finer lists would give.
+        BLOCK_Q = 128
     if md is None:                              # lines 157-158
         md = compute_mask_kernel(mask, BLOCK_Q, BLOCK_K)
     bits = getattr(md, "packed_bits", None)
-    q, k, v = _native._tma_ready(q), _native._tma_ready(k), _native._tma_ready(v)
-    impl_id = _native.IMPLS[impl]
     if bits is None and impl_id != _native.SA_IMPL_SIMT and \
             _native.uses_tcgen05(q, k, v, int(BLOCK_Q), int(BLOCK_K), True):
         # caller-supplied lists without the packed plane: derive the plane from the mask

@@ -183,3 +183,60 @@ def test_custom_ops_pass_opcheck(native_lib):
     args = (q, k, v, mask.expand(B, H, S, S), bits, ex(f_ids, 4), ex(f_lens, 3), ex(p_ids, 4), ex(p_lens, 3),
             128, 32, _native.SA_IMPL_AUTO, False)
     torch.library.opcheck(_native.attn_fwd_op, args, test_utils=checks)
+
+
+def test_both_stages_replay_from_a_cuda_graph(native_lib):
+    """Stage 1 + stage 2 captured once and replayed: nothing on the path allocates outside torch's
+    capture-aware allocator or synchronises, so a layer loop can replay it (the amortisation the
+    reference's README assumes when it quotes stage 2 alone)."""
+    B, H, S, D = 2, 4, 1024, 128
+    q, k, v = (t.to(DEV) for t in workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=21))
+    mask = workloads.random_block_mask(B, S, 0.6, 0.2, seed=22).to(DEV)
+
+    def both():
+        md = sa.compute_mask_kernel(mask.expand(B, H, S, S), 128, 32)
+        return sa.sparse_attention(q, k, v, mask, 128, 32, mask_metadata=md, check_status=False)
+
+    eager = both()                                  # also the warm-up the capture needs
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        both()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            out = both()
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    ref = sdpa_cpu(q.cpu(), k.cpu(), v.cpu(), mask.cpu())
+    assert_close_attn(out, ref, torch.bfloat16, "graph replay")
+
+
+def test_uneven_tiles_are_all_written(native_lib):
+    """Tiles of very different length (document mask: 1 to S/128 steps) with more tiles than SMs: the
+    CTAs draw tiles from the shared counter; every query block must come out once and right."""
+    B, H, S, D = 1, 6, 4096, 128                    # 6 * 32 = 192 tiles > 148 CTAs
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=31)
+    mask = workloads.document_causal_mask(B, S, (256, 2048), seed=32)
+    ref = sdpa_cpu(q, k, v, mask)
+    for _ in range(2):
+        out = _run(q, k, v, mask, 128, 32, impl="tcgen05")
+        assert_close_attn(out, ref, torch.bfloat16, "uneven tiles")
+
+
+@pytest.mark.parametrize("bq,bk", [(32, 32), (64, 64), (32, 128)])
+def test_finer_query_blocks_take_the_tensor_core_kernel(native_lib, bq, bk):
+    """BLOCK_Q of 32 / 64 (the reference's other defaults, test_attn.py:32) without caller lists: the
+    lists are built 128 rows high and the bit plane masks the elements -- same values as SDPA and as
+    the generic kernel walking the finer lists."""
+    B, H, S, D = 2, 2, 512, 128
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=bq + bk)
+    mask = workloads.random_block_mask(B, S, 0.5, 0.2, seed=bq)
+    ref = sdpa_cpu(q, k, v, mask)
+    out = _run(q, k, v, mask, bq, bk)
+    assert_close_attn(out, ref, torch.bfloat16, f"auto ({bq},{bk})")
+    fine = _run(q, k, v, mask, bq, bk, impl="simt")
+    assert_close_attn(out, fine.float().cpu(), torch.bfloat16, f"auto vs simt ({bq},{bk})")
