@@ -99,7 +99,8 @@ struct Smem {
   static constexpr uint32_t off_bits = off_v + kStagesV * kTileBytes;      // [kBitStages][4 sub-slots][128 rows] u32
   static constexpr uint32_t off_bar = off_bits + kBitStages * 4 * 128 * 4;
   static constexpr uint32_t off_misc = off_bar + 8 * 48;
-  static constexpr uint32_t off_xch = off_misc + 16 + 4 * kTileRing;   // misc: TMEM base, abort flag, tile ring             // [2 parities + epilogue][kSplit column groups][128 rows] f32
+  static constexpr uint32_t off_ids = off_misc + 16 + 4 * kTileRing;   // misc: TMEM base, abort flag, tile ring
+  static constexpr uint32_t off_xch = off_ids + 2 * 4 * 4 * 4;         // ids: per producer warp [4 steps][4 entries]; xch: [2 parities + epilogue][kSplit column groups][128 rows] f32
   static constexpr uint32_t total = off_xch + 3 * kSplit * 128 * 4;
 #ifdef SA_TRACE
   static constexpr uint32_t dynamic_bytes = total + 1024 + 5 * 500 * 8;
@@ -421,9 +422,12 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
     const uint32_t slot_bytes = static_cast<uint32_t>(p.BK) * 128u;
     constexpr int kPanels = D / 64;
     const int c_of_lane = lane / kPanels, pnl_of_lane = lane % kPanels;
+    const bool has_box = c_of_lane < eps;
     bool bad_index = false;
     bool ok = true;
     int st = 0, round = 0, gu = 0, tq = 0;
+    const uint32_t s_ids = sbase + L::off_ids + static_cast<uint32_t>(warp) * 64u;
+    const volatile int* ids_ring = reinterpret_cast<const volatile int*>(smem + L::off_ids + warp * 64);
     // lane 0 of warp 0 publishes tile `t` as ordinal `ord` of the sequence
     auto publish = [&](int ord, int t) {
       const int slot = ord % kTileRing;
@@ -469,18 +473,24 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       const int32_t* fids = p.full_ids + b * p.fis[0] + h * p.fis[1] + static_cast<int64_t>(qblk) * p.fis[2];
       const int32_t* pids = p.part_ids + b * p.pis[0] + h * p.pis[1] + static_cast<int64_t>(qblk) * p.pis[2];
       const uint32_t* bits_plane = p.bits + b * p.bits_sb + h * p.bits_sh;
-      // kv-block id of entry `lane` of step j (lanes >= entries per step hold 0)
-      auto my_id_of = [&](int j) -> int {
-        if (lane >= eps || j >= n_steps) return 0;
-        const int e = (j << eps_shift) + lane;
-        const int ee = e < total ? e : 0;           // slots past the end re-load the first listed block
-        int id = ee < n_full ? fids[ee * p.fis[3]] : pids[(ee - n_full) * p.pis[3]];   // line 33
-        if (static_cast<unsigned>(id) >= static_cast<unsigned>(nk)) { bad_index = true; id = 0; }
-        return id;
+      // The list entries of a step are copied to a four-step ring in shared memory two steps before
+      // they are needed, asynchronously (one group per step): nothing waits for the lists' latency.
+      auto fetch_ids = [&](int j) {
+        if (lane < eps && j < n_steps) {
+          const int e = (j << eps_shift) + lane;
+          const int ee = e < total ? e : 0;         // slots past the end re-load the first listed block
+          const int32_t* src = ee < n_full ? fids + ee * p.fis[3] : pids + (ee - n_full) * p.pis[3];   // line 33
+          ptx::cp_async_4(s_ids + static_cast<uint32_t>((j & 3) * 4 + lane) * 4u, src);
+        }
+        ptx::cp_async_commit();
       };
-      int id_cur = my_id_of(0), id_nxt = my_id_of(1);
+      __syncwarp();                                     // every lane has read the previous tile's last entries
+      fetch_ids(0);
+      fetch_ids(1);
       for (int j = 0; j < n_steps && ok; ++j) {
-        const int id_nxt2 = my_id_of(j + 2);            // fetched two steps before it is needed
+        fetch_ids(j + 2);
+        ptx::cp_async_wait<2>();                        // the group of step j has landed
+        __syncwarp();
         if (lane == 0) SA_TRACE_EVENT(warp, 0, j);
         const uint32_t dst = s_tiles + st * L::kTileBytes;
         const uint32_t full_bar = bar(bar_full + st);
@@ -488,7 +498,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         // S(j) is complete the softmax finds them in shared memory without a wait of its own.
         const bool with_bits = is_k && j >= n_plain;
         const int u = gu + (j - n_plain), bst = u % kBitStages;
-        uint32_t tx_bytes = (SA_DEBUG_FLAGS & 2) ? slot_bytes : L::kTileBytes;
+        uint32_t tx_bytes = L::kTileBytes;
         if (with_bits) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -504,14 +514,16 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (lane == 0) SA_TRACE_EVENT(warp, 1, j);
-        const int id_c = __shfl_sync(0xffffffffu, id_cur, c_of_lane & 3);
-        if (ok && c_of_lane < eps && (!(SA_DEBUG_FLAGS & 2) || lane == 0))
+        int id_c = ids_ring[(j & 3) * 4 + (c_of_lane & 3)];
+        if (static_cast<unsigned>(id_c) >= static_cast<unsigned>(nk)) { bad_index = bad_index || has_box; id_c = 0; }
+        if (ok && has_box)
           ptx::tma_load_4d(dst + pnl_of_lane * kPanelBytes + c_of_lane * slot_bytes, tm, full_bar,
                            pnl_of_lane * 64, id_c * p.BK, ch, cb);
         if (lane == 0) SA_TRACE_EVENT(warp, 2, j);
         if (with_bits) {
           const int c = lane & 3, ec = c >> sps_shift;
-          const int id_b = __shfl_sync(0xffffffffu, id_cur, ec);
+          int id_b = ids_ring[(j & 3) * 4 + ec];
+          if (static_cast<unsigned>(id_b) >= static_cast<unsigned>(nk)) id_b = 0;
           const int e = (j << eps_shift) + ec;
           if (ok && lane < 4 && e >= n_full && e < total) {
             const int64_t kb32 = (static_cast<int64_t>(id_b) << sps_shift) + (c & ((1 << sps_shift) - 1));
@@ -519,7 +531,6 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
             ptx::bulk_load(sBits + static_cast<uint32_t>(bst * 4 + c) * 512u, src, 512u, full_bar);
           }
         }
-        id_cur = id_nxt; id_nxt = id_nxt2;
         if (++st == n_stages) { st = 0; ++round; }
       }
       gu += n_steps - n_plain;
