@@ -95,6 +95,25 @@ int sa_classify_mask_static(const uint8_t* mask,
                             int32_t* part_ids, int32_t* part_lens,
                             uint32_t* packed_bits, void* stream);
 
+/* No counterpart in the reference.  Folds lists made for query blocks `ratio` times shorter than the
+ * ones wanted into lists for the tall blocks: a kv block is full for a tall block when it is in the
+ * full list of each of its `ratio` short blocks, partial when any of them lists it and it is not full.
+ * This is how lists built at BLOCK_Q = 32 or 64 (the reference's test_attn.py:32 uses (32, 128)) are
+ * brought to the 128-row tiles of the tcgen05 kernel; the packed bit plane masks the elements.
+ * Inputs: int32 [planes, nq_in, nk] ids and [planes, nq_in] lengths, contiguous; ids[..., :len] are
+ * read.  Outputs: [planes, nq_in / ratio, nk] ids (ascending, tails -1) and [planes, nq_in / ratio].
+ * packed_bits: optional plane [planes, nk * BLOCK_K / 32, nq_in * BLOCK_Q_in] made from the mask
+ *   (sa_classify_mask), modified in place: inside the tall partial tiles, rows of a short block that
+ *   does not list the kv block become all False and rows of one that lists it as full all True, so
+ *   that stage 2 computes what a walk over the short lists computes even when the caller has edited
+ *   them (lists derived from the same mask leave the plane unchanged). */
+int sa_merge_lists(const int32_t* full_ids_in, const int32_t* full_lens_in,
+                   const int32_t* part_ids_in, const int32_t* part_lens_in,
+                   int planes, int nq_in, int nk, int ratio, int BLOCK_Q_in, int BLOCK_K,
+                   int32_t* full_ids_out, int32_t* full_lens_out,
+                   int32_t* part_ids_out, int32_t* part_lens_out,
+                   uint32_t* packed_bits, void* stream);
+
 /* Whether SA_IMPL_AUTO would pick the tcgen05 kernel for this call (1) or the SIMT kernel (0). */
 int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int Sk,
                          const void* q, const void* k, const void* v,

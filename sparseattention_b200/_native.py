@@ -36,6 +36,7 @@ SYMBOLS = {
     "sa_classify_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "sa_classify_mask": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
     "sa_classify_mask_static": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
+    "sa_merge_lists": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "sa_attn_uses_tcgen05": (_i, [_i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i]),
     "sa_attn_fwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p,
                          _i, _i, _i, _i, _i, _i, _i, _i,
@@ -174,6 +175,27 @@ def classify(mask: torch.Tensor, block_q: int, block_k: int, with_bits: bool = T
     if mask.dim() != 4:
         raise ValueError("mask must be [B,H,Sq,Sk]")
     return classify_mask_op(_canonical_mask(mask), int(block_q), int(block_k), bool(with_bits))
+
+
+def merge_lists(full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
+                block_q_in: int, block_k: int, ratio: int, bits: torch.Tensor):
+    """Lists for query blocks of ``block_q_in`` rows ([P0,P1,nq_in,nk] / [P0,P1,nq_in], contiguous int32,
+    distinct planes only) -> lists for blocks ``ratio`` times taller.  ``bits`` ([P0,P1,Sk/32,Sq]) is
+    patched in place so that it says what the short lists say (see ``sa_merge_lists``)."""
+    _require_cuda(full_ids, full_lens, part_ids, part_lens, bits)
+    lib = load_library()
+    P0, P1, nq_in, nk = full_ids.shape
+    dev = full_ids.device
+    with torch.cuda.device(dev):
+        out_ids = lambda: torch.empty((P0, P1, nq_in // ratio, nk), dtype=torch.int32, device=dev)
+        out_lens = lambda: torch.empty((P0, P1, nq_in // ratio), dtype=torch.int32, device=dev)
+        f_ids, p_ids, f_lens, p_lens = out_ids(), out_ids(), out_lens(), out_lens()
+        rc = lib.sa_merge_lists(full_ids.data_ptr(), full_lens.data_ptr(), part_ids.data_ptr(), part_lens.data_ptr(),
+                                P0 * P1, nq_in, nk, ratio, block_q_in, block_k,
+                                f_ids.data_ptr(), f_lens.data_ptr(), p_ids.data_ptr(), p_lens.data_ptr(),
+                                bits.data_ptr(), _stream_ptr(dev))
+    _check(rc, "sa_merge_lists")
+    return f_ids, f_lens, p_ids, p_lens
 
 
 # ------------------------------------------------------------------------------- stage 2

@@ -76,6 +76,29 @@ int sa_classify_mask(const uint8_t* mask,
   return sa::launch_classify(p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 
+int sa_merge_lists(const int32_t* full_ids_in, const int32_t* full_lens_in,
+                   const int32_t* part_ids_in, const int32_t* part_lens_in,
+                   int planes, int nq_in, int nk, int ratio, int BLOCK_Q_in, int BLOCK_K,
+                   int32_t* full_ids_out, int32_t* full_lens_out,
+                   int32_t* part_ids_out, int32_t* part_lens_out,
+                   uint32_t* packed_bits, void* stream) {
+  if (full_ids_in == nullptr || full_lens_in == nullptr || part_ids_in == nullptr || part_lens_in == nullptr ||
+      full_ids_out == nullptr || full_lens_out == nullptr || part_ids_out == nullptr || part_lens_out == nullptr)
+    return SA_ERR_INVALID_ARGUMENT;
+  if (!positive(planes) || !positive(nq_in) || !positive(nk) || !positive(ratio) || nq_in % ratio != 0 ||
+      !positive(BLOCK_Q_in) || !positive(BLOCK_K))
+    return SA_ERR_INVALID_ARGUMENT;
+  if (BLOCK_Q_in % sa::kCell != 0 || BLOCK_K % sa::kCell != 0) return SA_ERR_UNSUPPORTED;
+  if (static_cast<size_t>(ratio) * static_cast<size_t>(nk) > 40u * 1024u) return SA_ERR_UNSUPPORTED;
+  if (static_cast<long long>(planes) * (nq_in / ratio) > 0x7fffffffLL) return SA_ERR_UNSUPPORTED;
+  sa::ClassifyParams p = {};
+  p.full_ids = full_ids_out; p.full_lens = full_lens_out; p.part_ids = part_ids_out; p.part_lens = part_lens_out;
+  p.bits = packed_bits;
+  return sa::launch_merge_lists(full_ids_in, full_lens_in, part_ids_in, part_lens_in, planes, nq_in / ratio, nk,
+                                ratio, BLOCK_Q_in, BLOCK_K, p, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? SA_OK : SA_ERR_CUDA;
+}
+
 static int fill_attn_params(sa::AttnParams& p,
                             const void* q, const void* k, const void* v, void* o,
                             const int64_t* q_strides, const int64_t* k_strides,

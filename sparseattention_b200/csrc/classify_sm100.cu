@@ -104,21 +104,16 @@ classify_cells_kernel(const ClassifyParams p, const int chunks_per_row, const lo
 
 constexpr int kListsThreads = 128;
 
-// One CTA per (mask plane, query block): 128 tiles per pass, one per thread; the order of the ids
-// (ascending kv block, mask_utils.py:66-79) comes from a ballot within each warp and a prefix over
-// the four warps.
-__global__ void __launch_bounds__(kListsThreads)
-compact_lists_kernel(const ClassifyParams p, const int n_rows) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");     // the cell flags of the streaming kernel are complete
-  __shared__ int s_full[kListsThreads / 32], s_part[kListsThreads / 32];
+// Folds the flags of the BLOCK_Q x BLOCK_K tiles of one query block (flags[y * flag_pitch + x] for the
+// 32 x 32 cell (y, x) of the block: bit 0 = any True, bit 1 = all True) and writes the block's two
+// ascending id lists, their -1 tails and lengths.  128 tiles per pass, one per thread; the order of
+// the ids (ascending kv block, mask_utils.py:66-79) comes from a ballot within each warp and a prefix
+// over the four warps.  Called by all kListsThreads threads of a CTA.
+__device__ __forceinline__ void build_lists(const ClassifyParams& p, const uint8_t* flags, int64_t flag_pitch,
+                                            int row, int* s_full, int* s_part) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int row = blockIdx.x;                                       // (plane, query block)
-  if (row >= n_rows) return;
-  const int nq = p.Sq / p.BQ, nk = p.Sk / p.BK;
+  const int nk = p.Sk / p.BK;
   const int rq = p.BQ / kCell, rk = p.BK / kCell;
-  const int row_cells = p.Sq / kCell, col_cells = p.Sk / kCell;
-  const int plane = row / nq, i = row % nq;
-  const uint8_t* cells = p.cells + (static_cast<int64_t>(plane) * row_cells + static_cast<int64_t>(i) * rq) * col_cells;
   int32_t* f_out = p.full_ids + static_cast<int64_t>(row) * nk;
   int32_t* p_out = p.part_ids + static_cast<int64_t>(row) * nk;
   const uint32_t lt_mask = (1u << lane) - 1u;
@@ -128,7 +123,7 @@ compact_lists_kernel(const ClassifyParams p, const int n_rows) {
     uint32_t any = 0u, all = 2u;
     if (j < nk) {
       for (int y = 0; y < rq; ++y) {
-        const uint8_t* c = cells + static_cast<int64_t>(y) * col_cells + static_cast<int64_t>(j) * rk;
+        const uint8_t* c = flags + static_cast<int64_t>(y) * flag_pitch + static_cast<int64_t>(j) * rk;
         for (int x = 0; x < rk; ++x) {
           const uint32_t f = c[x];
           any |= f;
@@ -160,6 +155,79 @@ compact_lists_kernel(const ClassifyParams p, const int n_rows) {
   if (tid == 0) {
     p.full_lens[row] = nf;                                       // mask_utils.py:81
     p.part_lens[row] = np;                                       // mask_utils.py:82
+  }
+}
+
+// One CTA per (mask plane, query block).
+__global__ void __launch_bounds__(kListsThreads)
+compact_lists_kernel(const ClassifyParams p, const int n_rows) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");     // the cell flags of the streaming kernel are complete
+  __shared__ int s_full[kListsThreads / 32], s_part[kListsThreads / 32];
+  const int row = blockIdx.x;                                       // (plane, query block)
+  if (row >= n_rows) return;
+  const int nq = p.Sq / p.BQ, rq = p.BQ / kCell;
+  const int row_cells = p.Sq / kCell, col_cells = p.Sk / kCell;
+  const int plane = row / nq, i = row % nq;
+  const uint8_t* cells = p.cells + (static_cast<int64_t>(plane) * row_cells + static_cast<int64_t>(i) * rq) * col_cells;
+  build_lists(p, cells, col_cells, row, s_full, s_part);
+}
+
+// Lists of short query blocks -> lists of the tall query blocks that contain `ratio` of them each.
+// One CTA per tall block: the short blocks' lists are scattered into per-(short block, kv block)
+// flags in shared memory (3 = in the full list, 1 = in the partial list, 0 = not listed), which
+// build_lists folds like cell flags: full for the tall block if full for every short block,
+// partial if listed by any.  Dynamic shared memory: ratio * nk bytes.
+//
+// With a bit plane (p_out.bits, [planes, Sk/32, Sq], made from the mask) the kernel also makes the
+// plane say what the short lists say, for the tiles stage 2 will read it for (the tall partial ones):
+// rows of a short block that does not list the kv block become all False, rows of one that lists it
+// as full become all True.  For lists that were derived from the same mask this rewrites words with
+// the value they already have; for lists a caller has pruned or widened it is what keeps the result
+// equal to walking the short lists (sparse_attn_kernel.py:113-142).  bq_in, bk: the short lists' block sizes.
+__global__ void __launch_bounds__(kListsThreads)
+merge_lists_kernel(const ClassifyParams p_out, const int32_t* __restrict__ full_ids_in,
+                   const int32_t* __restrict__ full_lens_in, const int32_t* __restrict__ part_ids_in,
+                   const int32_t* __restrict__ part_lens_in, const int nq_out, const int nk, const int ratio,
+                   const int bq_in, const int bk) {
+  extern __shared__ uint8_t s_listed[];
+  __shared__ int s_full[kListsThreads / 32], s_part[kListsThreads / 32];
+  const int tid = threadIdx.x;
+  const int row = blockIdx.x;                                       // (plane, tall query block)
+  const int plane = row / nq_out, i = row % nq_out;
+  for (int t = tid; t < ratio * nk; t += kListsThreads) s_listed[t] = 0;
+  __syncthreads();
+  for (int s = 0; s < ratio; ++s) {
+    const int64_t row_in = (static_cast<int64_t>(plane) * nq_out + i) * ratio + s;
+    const int nf = min(max(full_lens_in[row_in], 0), nk), np = min(max(part_lens_in[row_in], 0), nk);
+    for (int t = tid; t < nf; t += kListsThreads) {
+      const int id = full_ids_in[row_in * nk + t];
+      if (static_cast<unsigned>(id) < static_cast<unsigned>(nk)) s_listed[s * nk + id] = 3;
+    }
+    for (int t = tid; t < np; t += kListsThreads) {
+      const int id = part_ids_in[row_in * nk + t];
+      if (static_cast<unsigned>(id) < static_cast<unsigned>(nk)) s_listed[s * nk + id] = 1;
+    }
+  }
+  __syncthreads();
+  build_lists(p_out, s_listed, nk, row, s_full, s_part);
+  if (p_out.bits == nullptr) return;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int wpb = bk / kCell;                                       // 32-column word groups per kv block
+  uint32_t* plane_bits = p_out.bits + static_cast<int64_t>(plane) * (static_cast<int64_t>(nk) * wpb) * p_out.Sq;
+  const int row0 = i * ratio * bq_in;                               // first query row of the tall block
+  for (int j = warp; j < nk; j += kListsThreads / 32) {
+    uint32_t any = 0u, all = 2u;
+    for (int s = 0; s < ratio; ++s) { any |= s_listed[s * nk + j]; all &= s_listed[s * nk + j]; }
+    if ((all & 2u) || !(any & 1u)) continue;                        // tall-full or not listed: the plane is not read
+    for (int s = 0; s < ratio; ++s) {
+      const uint32_t f = s_listed[s * nk + j];
+      if (f == 1u) continue;                                        // listed as partial: the mask's own bits
+      const uint32_t word = f == 3u ? 0xffffffffu : 0u;
+      for (int x = 0; x < wpb; ++x) {
+        uint32_t* dst = plane_bits + (static_cast<int64_t>(j) * wpb + x) * p_out.Sq + row0 + s * bq_in;
+        for (int r = lane; r < bq_in; r += 32) dst[r] = word;
+      }
+    }
   }
 }
 
@@ -202,6 +270,21 @@ cudaError_t launch_classify(const ClassifyParams& p, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, compact_lists_kernel, p, n_rows);
+}
+
+// p_out carries only the output pointers; its block sizes are set here so that build_lists sees one
+// flag row per short block and one flag per kv block.
+cudaError_t launch_merge_lists(const int32_t* full_ids_in, const int32_t* full_lens_in, const int32_t* part_ids_in,
+                               const int32_t* part_lens_in, int planes, int nq_out, int nk, int ratio,
+                               int bq_in, int bk, ClassifyParams p_out, cudaStream_t stream) {
+  p_out.BQ = kCell * ratio;
+  p_out.BK = kCell;
+  p_out.Sk = kCell * nk;
+  p_out.Sq = nq_out * ratio * bq_in;
+  const size_t smem = static_cast<size_t>(ratio) * static_cast<size_t>(nk);
+  merge_lists_kernel<<<static_cast<unsigned>(planes * nq_out), kListsThreads, smem, stream>>>(
+      p_out, full_ids_in, full_lens_in, part_ids_in, part_lens_in, nq_out, nk, ratio, bq_in, bk);
+  return cudaGetLastError();
 }
 
 }  // namespace sa

@@ -26,6 +26,10 @@ struct ClassifyParams {
 };
 
 cudaError_t launch_classify(const ClassifyParams& p, cudaStream_t stream);
+// Lists of query blocks `ratio` times shorter -> lists of the tall blocks (p_out: output pointers only).
+cudaError_t launch_merge_lists(const int32_t* full_ids_in, const int32_t* full_lens_in, const int32_t* part_ids_in,
+                               const int32_t* part_lens_in, int planes, int nq_out, int nk, int ratio,
+                               int bq_in, int bk, ClassifyParams p_out, cudaStream_t stream);
 
 // ---------------------------------------------------------------- stage 2
 struct AttnParams {

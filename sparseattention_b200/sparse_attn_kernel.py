@@ -19,6 +19,36 @@ def _no_bits(device) -> torch.Tensor:
     return t
 
 
+def _distinct(t: torch.Tensor) -> torch.Tensor:
+    """The distinct leading planes of a list tensor that may be an expanded view."""
+    bu = 1 if (t.shape[0] == 1 or t.stride(0) == 0) else t.shape[0]
+    hu = 1 if (t.shape[1] == 1 or t.stride(1) == 0) else t.shape[1]
+    return t[:bu, :hu]
+
+
+def _merged_to_128(md: MaskMetadata, mask: torch.Tensor, block_q: int, block_k: int):
+    """Caller-supplied lists for BLOCK_Q = 32 / 64 (test_attn.py:32 builds them at (32, 128)) folded
+    into lists for the 128-row tiles of the tensor-core kernel, with a bit plane made from the mask and
+    brought in line with the lists, so that the result is the one a walk over the given lists gives.
+    None when the lists and the mask are broadcast differently (the generic kernel then runs)."""
+    lists = [_distinct(t) for t in (md.unmasked_kv_ids, md.unmasked_lens, md.masked_kv_ids, md.masked_lens)]
+    planes = tuple(lists[0].shape[:2])
+    if any(tuple(t.shape[:2]) != planes for t in lists):
+        return None
+    bits = _native.classify(mask, 128, block_k, with_bits=True)[4]          # fresh: it is patched below
+    bu, hu = bits.shape[0], bits.shape[1]
+    if planes[0] not in (1, bu) or planes[1] not in (1, hu):
+        return None
+    lists = [t.expand(bu, hu, *t.shape[2:]).to(torch.int32).contiguous() for t in lists]
+    f_ids, f_lens, p_ids, p_lens = _native.merge_lists(lists[0], lists[1], lists[2], lists[3],
+                                                       block_q, block_k, 128 // block_q, bits)
+    B, H, Sq, Sk = mask.shape
+    nq, nk = Sq // 128, Sk // block_k
+    return MaskMetadata(f_ids.expand(B, H, nq, nk), f_lens.expand(B, H, nq),
+                        p_ids.expand(B, H, nq, nk), p_lens.expand(B, H, nq),
+                        packed_bits=bits, block_sizes=(128, block_k))
+
+
 def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, BLOCK_Q, BLOCK_K,
                      mask_metadata: MaskMetadata = None, *, impl: str = "auto", check_status: bool = None):
     """Block-sparse attention forward: ``softmax(q k^T / sqrt(D) + where(mask, 0, -inf)) v``
@@ -26,8 +56,8 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     not given), exactly the call of sparse_attn_kernel.py:149.
 
     q: ``[B,H,Sq,D]``; k, v: ``[B,H,Sk,D]``; mask: bool, broadcastable to ``[B,H,Sq,Sk]``.
-    fp16 / bf16 with D in {64,128}, BLOCK_Q = 128 (or 32 / 64 when the lists are built here rather
-    than supplied) and BLOCK_K in {32,64,128} run the TMA + tcgen05 kernel; every other
+    fp16 / bf16 with D in {64,128}, BLOCK_Q = 128 (or 32 / 64: lists for those are built, or folded
+    from the caller's, at 128 rows) and BLOCK_K in {32,64,128} run the TMA + tcgen05 kernel; every other
     combination of fp32 / fp16 / bf16, D in {16,32,64,128} and block sizes that are multiples of
     32 runs the generic CUDA-core kernel.  ``impl``
     ("auto" | "tcgen05" | "simt") forces one of them.  Rows whose mask is all False return 0.
@@ -52,6 +82,11 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
         # BLOCK_Q-row blocks would be, and the bit plane masks the elements, so the result is the
         # one the finer lists would give.
         BLOCK_Q = 128
+    if md is not None and int(BLOCK_Q) in (32, 64) and impl_id != _native.SA_IMPL_SIMT and \
+            _native.uses_tcgen05(q, k, v, 128, int(BLOCK_K), True):
+        merged = _merged_to_128(md, mask, int(BLOCK_Q), int(BLOCK_K))
+        if merged is not None:
+            md, BLOCK_Q = merged, 128
     if md is None:                              # lines 157-158
         md = compute_mask_kernel(mask, BLOCK_Q, BLOCK_K)
     bits = getattr(md, "packed_bits", None)

@@ -240,3 +240,44 @@ def test_finer_query_blocks_take_the_tensor_core_kernel(native_lib, bq, bk):
     assert_close_attn(out, ref, torch.bfloat16, f"auto ({bq},{bk})")
     fine = _run(q, k, v, mask, bq, bk, impl="simt")
     assert_close_attn(out, fine.float().cpu(), torch.bfloat16, f"auto vs simt ({bq},{bk})")
+
+
+@pytest.mark.parametrize("bq,bk", [(32, 128), (64, 32), (32, 32)])
+def test_caller_lists_for_short_query_blocks_are_folded(native_lib, bq, bk):
+    """Lists supplied by the caller for BLOCK_Q = 32 / 64 -- the way the reference's own harness calls it
+    (test_attn.py:38-41, lists built at (32, 128) and passed in): folded into 128-row lists on the device.
+    The folded lists must be the ones the classifier gives at 128 rows, and the values those of SDPA."""
+    B, H, S, D = 2, 3, 1024, 128
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=3 * bq + bk)
+    mask = workloads.random_block_mask(B, S, 0.5, 0.2, seed=bq + 7).to(DEV)
+    md = sa.compute_mask_kernel(mask.expand(B, H, S, S), bq, bk)
+    short = [t[:, :1].contiguous() for t in (md.unmasked_kv_ids, md.unmasked_lens, md.masked_kv_ids, md.masked_lens)]
+    f128, fl128, p128, pl128, bits = _native.classify(mask, 128, bk, with_bits=True)
+    before = bits.clone()
+    f_ids, f_lens, p_ids, p_lens = _native.merge_lists(*short, bq, bk, 128 // bq, bits)
+    torch.cuda.synchronize()
+    assert torch.equal(f_lens, fl128) and torch.equal(p_lens, pl128)
+    assert torch.equal(f_ids, f128) and torch.equal(p_ids, p128)          # tails are -1 in both
+    assert torch.equal(bits, before)                                      # lists from the same mask: no change
+    ref = sdpa_cpu(q, k, v, mask.cpu())
+    md.packed_bits = None                                                 # as if the reference had made it
+    out = _run(q, k, v, mask, bq, bk, md=md)
+    assert_close_attn(out, ref, torch.bfloat16, f"folded ({bq},{bk})")
+
+
+def test_pruned_caller_lists_are_honoured_after_folding(native_lib):
+    """A caller that drops kv blocks from the short lists (block selection on top of the mask) gets what a
+    walk over those lists gives -- the generic kernel is that walk -- not what the mask alone would give."""
+    B, H, S, D, bq, bk = 1, 2, 1024, 128, 32, 32
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=77)
+    mask = workloads.random_block_mask(B, S, 0.3, 0.2, seed=78).to(DEV)
+    md = sa.compute_mask_kernel(mask.expand(B, H, S, S), bq, bk)
+    # drop the last listed block of every list that has more than one entry
+    md.unmasked_lens = torch.where(md.unmasked_lens > 1, md.unmasked_lens - 1, md.unmasked_lens).contiguous()
+    md.masked_lens = torch.where(md.masked_lens > 1, md.masked_lens - 1, md.masked_lens).contiguous()
+    md.packed_bits = None
+    walk = _run(q, k, v, mask, bq, bk, impl="simt", md=md).float().cpu()
+    out = _run(q, k, v, mask, bq, bk, md=md)
+    assert_close_attn(out, walk, torch.bfloat16, "pruned lists")
+    full = sdpa_cpu(q, k, v, mask.cpu())
+    assert (walk - full).abs().max().item() > 5e-2          # the pruning does change the answer
