@@ -374,7 +374,7 @@ def run_ours(args):
                        "shard": "each rank owns a full (batch, head) shard of the workload"},
             "roofline": {"bound": "tensor", "achieved": att_tflops, "peak": peaks["bf16_tflops_sustained"],
                          "unit": "TFLOP/s", "frac": att_tflops / peaks["bf16_tflops_sustained"],
-                         "traffic": 256.7e6 * B / 2.0, "traffic_unit": "bytes per launch (ncu capture at B=2, p=0.5, scaled by batch)",
+                         "traffic": 254.3e6 * B / 2.0, "traffic_unit": "bytes per launch (ncu capture at B=2, p=0.5, scaled by batch)",
                          "kernel": "attn_fwd_tc_kernel<bf16,128>", "peak_source": peak_kind + " (sustained bf16 matmul)",
                          "note": "FLOPs of the listed tiles of all six launches / sum of their durations (CUDA events)"},
             "roofline_classifier": {"bound": "hbm", "achieved": cls_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -390,12 +390,48 @@ def run_ours(args):
             "gpu_launches": args.steps * n_p * 3,
             "clocks": clocks,
         }
+        if world == 1 and args.comparators:
+            line["comparators"] = gpu_comparators(q, k, v, masks, ps, flops_p)
         if world == 1 and not args.no_cpu_baseline:
             val, sec, desc, cores = cpu_sample(args.cpu_heads, 1, 1)
             line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
+
+
+def gpu_comparators(q, k, v, masks, ps, flops_p):
+    """Same-box library comparators of the reference's harness (test_attn.py:64): torch SDPA without a
+    mask (the vendor's dense kernel) and with the bool mask, timed like the reference times them (CUDA
+    events, best of a few runs).  Off by default; the figures are not part of the metric."""
+    import torch
+    import torch.nn.functional as F
+
+    def best_ms(fn, n=5, warm=2):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(n):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return min(ts)
+
+    B, H, S, D = q.shape
+    dense = 4.0 * B * H * S * S * D
+    out = {}
+    t = best_ms(lambda: F.scaled_dot_product_attention(q, k, v))
+    out["sdpa_dense"] = {"ms": t, "tflops_dense": dense / (t * 1e-3) / 1e12}
+    rows = []
+    for p, m, fl in zip(ps, masks, flops_p):
+        try:
+            t = best_ms(lambda: F.scaled_dot_product_attention(q, k, v, attn_mask=m), n=3, warm=1)
+            rows.append({"p": p, "ms": t, "tflops_listed_tiles": fl / (t * 1e-3) / 1e12})
+        except Exception as e:                      # a backend that cannot take the mask
+            rows.append({"p": p, "unavailable": repr(e)[:120]})
+    out["sdpa_bool_mask"] = rows
+    return out
 
 
 def _quiet_stdout():
@@ -415,6 +451,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-heads", type=int, default=4, help="heads in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--comparators", action="store_true",
+                    help="N=1: also time torch SDPA (dense, and with the bool mask) on the same inputs")
     ap.add_argument("--profile", action="store_true",
                     help="profiling run: kernels only (no end-to-end leg, no CPU baseline, no warm-up floor)")
     ap.add_argument("--workload", default="headline", choices=["headline", "document", "composed", "scaling"],
