@@ -281,3 +281,15 @@ def test_pruned_caller_lists_are_honoured_after_folding(native_lib):
     assert_close_attn(out, walk, torch.bfloat16, "pruned lists")
     full = sdpa_cpu(q, k, v, mask.cpu())
     assert (walk - full).abs().max().item() > 5e-2          # the pruning does change the answer
+
+
+def test_without_a_workspace_the_tiles_are_dealt_round_robin(native_lib, monkeypatch):
+    """sa_attn_fwd with workspace = NULL (a host that binds the C ABI without one): the CTAs step through
+    the tiles by the grid size instead of drawing them from the counter; same values."""
+    B, H, S, D = 1, 6, 4096, 128                    # 192 tiles > 148 CTAs
+    q, k, v = workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=41)
+    mask = workloads.document_causal_mask(B, S, (256, 2048), seed=42)
+    with_ws = _run(q, k, v, mask, 128, 32, impl="tcgen05")
+    monkeypatch.setattr(native_lib, "sa_attn_workspace_bytes", lambda: 0)
+    without = _run(q, k, v, mask, 128, 32, impl="tcgen05")
+    assert torch.equal(with_ws, without)
