@@ -138,6 +138,9 @@ size_t sa_attn_workspace_bytes(void);
  *   3 element strides (b,h,q).  Only ids[..., :len] is read; they are trusted like the
  *   reference trusts a caller-supplied MaskMetadata (sparse_attn_kernel.py:157-163).
  * scale_log2: softmax scale already multiplied by log2(e) (sparse_attn_kernel.py:152).
+ * lse: optional float32 [B,H,Sq] contiguous (no counterpart in the reference, which lists it as future
+ *   work for a backward pass): per query row, log(sum over attended keys of exp(q.k * scale)), natural
+ *   log; -inf for a row with no attended key.
  * workspace: optional sa_attn_workspace_bytes() bytes of device memory, 4-byte aligned; the call clears
  *   it on the stream.  NULL (or too small): the tiles are dealt to the CTAs in a fixed round-robin order.
  *   Calls that may overlap on the GPU need a workspace each.
@@ -152,7 +155,7 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int32_t* full_lens, const int64_t* full_lens_strides,
                 const int32_t* part_ids, const int64_t* part_ids_strides,
                 const int32_t* part_lens, const int64_t* part_lens_strides,
-                float scale_log2, int impl, void* workspace, size_t workspace_bytes,
+                float scale_log2, int impl, float* lse, void* workspace, size_t workspace_bytes,
                 int32_t* dev_status, void* stream);
 
 #ifdef __cplusplus

@@ -42,7 +42,7 @@ SYMBOLS = {
                          _i, _i, _i, _i, _i, _i, _i, _i,
                          _p, _p, _p, _i64, _i64,
                          _p, _p, _p, _p, _p, _p, _p, _p,
-                         _f, _i, _p, _sz, _p, _p]),
+                         _f, _i, _p, _p, _sz, _p, _p]),
     "sa_attn_workspace_bytes": (_sz, []),
 }
 
@@ -210,10 +210,13 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 @torch.library.custom_op("sparseattention_b200::attn_fwd", mutates_args=())
 def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, bits: torch.Tensor,
                 full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
-                block_q: int, block_k: int, impl: int, check_status: bool) -> torch.Tensor:
+                block_q: int, block_k: int, impl: int, check_status: bool,
+                with_lse: bool) -> Tuple[torch.Tensor, torch.Tensor]:
     """Block-sparse attention forward over precomputed lists.  ``mask`` [B,H,Sq,Sk] and the
     list tensors ([B,H,nq,nk] / [B,H,nq]) may be expanded views; ``bits`` is the packed plane
-    [Bu,Hu,Sk/32,Sq] (or an empty tensor when absent)."""
+    [Bu,Hu,Sk/32,Sq] (or an empty tensor when absent).  Returns (O, LSE): LSE is float32 [B,H,Sq],
+    the natural-log sum of exp of a row's scaled scores over its attended keys (-inf for none), or
+    an empty tensor when ``with_lse`` is False."""
     _require_cuda(q, k, v, mask, full_ids, full_lens, part_ids, part_lens)
     lib = load_library()
     B, H, Sq, D = q.shape
@@ -237,6 +240,7 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
         else:
             bsb = bsh = 0
         status = torch.zeros((1,), dtype=torch.int32, device=dev) if check_status else None
+        lse = torch.empty((B, H, Sq) if with_lse else (0,), dtype=torch.float32, device=dev)
         ws_bytes = int(lib.sa_attn_workspace_bytes())
         ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)        # cleared by the call
         rc = lib.sa_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
@@ -246,7 +250,7 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
                              bits.data_ptr() if has_bits else None, bsb, bsh,
                              full_ids.data_ptr(), _strides(full_ids), full_lens.data_ptr(), _strides(full_lens),
                              part_ids.data_ptr(), _strides(part_ids), part_lens.data_ptr(), _strides(part_lens),
-                             scale_log2, impl, ws.data_ptr(), ws_bytes,
+                             scale_log2, impl, lse.data_ptr() if with_lse else None, ws.data_ptr(), ws_bytes,
                              status.data_ptr() if check_status else None, _stream_ptr(dev))
     _check(rc, "sa_attn_fwd")
     if check_status:
@@ -255,12 +259,14 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
             raise RuntimeError({SA_DEV_WAIT_EXPIRED: "attention kernel: a bounded device-side wait expired",
                                 SA_DEV_BAD_INDEX: "attention kernel: kv-block id out of range in a list"}.get(
                                     code, f"attention kernel: device status {code}"))
-    return o
+    return o, lse
 
 
 @attn_fwd_op.register_fake
-def _(q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, block_k, impl, check_status):
-    return q.new_empty(q.shape)
+def _(q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, block_k, impl, check_status,
+      with_lse):
+    B, H, Sq, _ = q.shape
+    return q.new_empty(q.shape), q.new_empty((B, H, Sq) if with_lse else (0,), dtype=torch.float32)
 
 
 def uses_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q: int, block_k: int,

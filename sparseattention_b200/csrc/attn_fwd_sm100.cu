@@ -691,9 +691,12 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       T* o_base = static_cast<T*>(p.o) + ti.b * p.os[0] + ti.h * p.os[1] +
                   static_cast<int64_t>(ti.qblk) * kTileM * p.os[2];
       uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + kOC * quarter);
+      float* lse_row = p.lse == nullptr ? nullptr
+          : p.lse + (static_cast<int64_t>(ti.b) * p.H + ti.h) * p.Sq + ti.qblk * kTileM + row;
       if (total == 0) {                            // nothing attended: the rows are 0
 #pragma unroll
         for (int i = 0; i < kOC / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (lse_row != nullptr && quarter == 0) *lse_row = -INFINITY;
         continue;
       }
       float m = -INFINITY, l = 0.f;                // lines 103-104; l holds this group's partial sum
@@ -812,6 +815,8 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
 #pragma unroll
       for (int q = 1; q < kSplit; ++q) l_row += xl[128 * q + row];
       const float inv = l_row > 0.f ? 1.f / l_row : 0.f;            // line 144, with 0 for an empty row
+      if (lse_row != nullptr && quarter == 0)      // m and l are in base 2 (scale folded, line 152)
+        *lse_row = l_row > 0.f ? (m + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
       uint32_t ro[kOC];
 #pragma unroll
       for (int c = 0; c < kOC / kOChunk; ++c) {

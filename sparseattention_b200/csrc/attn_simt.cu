@@ -127,6 +127,8 @@ attn_simt_kernel(const AttnParams p) {
   }
 
   const float inv = l > 0.f ? 1.f / l : 0.f;                                            // line 144
+  if (p.lse != nullptr && ql == 0)                 // m and l are in base 2 (scale folded, line 152)
+    p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Sq + row] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
   T* o = static_cast<T*>(p.o) + b * p.os[0] + h * p.os[1] + static_cast<int64_t>(row) * p.os[2];
 #pragma unroll
   for (int j = 0; j < DQ; ++j) o[static_cast<int64_t>(4 * j + ql) * p.os[3]] = from_f32<T>(acc[j] * inv);  // line 146

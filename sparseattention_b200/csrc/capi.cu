@@ -149,7 +149,7 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int32_t* full_lens, const int64_t* full_lens_strides,
                 const int32_t* part_ids, const int64_t* part_ids_strides,
                 const int32_t* part_lens, const int64_t* part_lens_strides,
-                float scale_log2, int impl, void* workspace, size_t workspace_bytes,
+                float scale_log2, int impl, float* lse, void* workspace, size_t workspace_bytes,
                 int32_t* dev_status, void* stream) {
   sa::AttnParams p;
   if (o == nullptr || o_strides == nullptr) return SA_ERR_INVALID_ARGUMENT;
@@ -169,6 +169,7 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   p.part_ids = part_ids; copy_n(p.pis, part_ids_strides, 4);
   p.part_lens = part_lens; copy_n(p.pls, part_lens_strides, 3);
   p.scale_log2 = scale_log2;
+  p.lse = lse;
   p.dev_status = dev_status;
   p.tile_counter = nullptr;
   if (workspace != nullptr && workspace_bytes >= sa_attn_workspace_bytes() &&

@@ -44,6 +44,7 @@ struct AttnParams {
   int B, H, Sq, Sk, D, BQ, BK;
   int dtype;
   float scale_log2;
+  float* lse;                                    // optional [B,H,Sq] contiguous: natural-log sum of exp of the scaled scores
   int32_t* dev_status;
   int32_t* tile_counter;                         // zeroed device word for the tile scheduler, or null (static order)
   int debug;

@@ -50,7 +50,8 @@ def _merged_to_128(md: MaskMetadata, mask: torch.Tensor, block_q: int, block_k: 
 
 
 def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, BLOCK_Q, BLOCK_K,
-                     mask_metadata: MaskMetadata = None, *, impl: str = "auto", check_status: bool = None):
+                     mask_metadata: MaskMetadata = None, *, impl: str = "auto", check_status: bool = None,
+                     return_lse: bool = False):
     """Block-sparse attention forward: ``softmax(q k^T / sqrt(D) + where(mask, 0, -inf)) v``
     computed only over the kv blocks listed in ``mask_metadata`` (built from the mask when
     not given), exactly the call of sparse_attn_kernel.py:149.
@@ -61,6 +62,10 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     combination of fp32 / fp16 / bf16, D in {16,32,64,128} and block sizes that are multiples of
     32 runs the generic CUDA-core kernel.  ``impl``
     ("auto" | "tcgen05" | "simt") forces one of them.  Rows whose mask is all False return 0.
+
+    ``return_lse=True`` returns ``(out, lse)`` with ``lse`` float32 ``[B,H,Sq]``: the natural-log sum of
+    exp of each row's scaled scores over its attended keys (-inf for a row with none) -- what a backward
+    pass or a merge of partial attentions needs; the reference does not produce it.
 
     ``check_status`` (default: the SPARSEATTN_B200_CHECK environment variable) makes the call
     read the kernel's device status word back, which synchronises; by default the call is
@@ -101,8 +106,9 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
         t = t if t.dtype == torch.int32 else t.to(torch.int32)
         return t.expand(*((B, H) + tuple(t.shape[2:]))) if t.dim() == nd else t
 
-    return _native.attn_fwd_op(
+    out, lse = _native.attn_fwd_op(
         q, k, v, mask, bits,
         lists(md.unmasked_kv_ids, 4), lists(md.unmasked_lens, 3),
         lists(md.masked_kv_ids, 4), lists(md.masked_lens, 3),
-        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status))
+        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status), bool(return_lse))
+    return (out, lse) if return_lse else out

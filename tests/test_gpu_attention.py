@@ -181,7 +181,7 @@ def test_custom_ops_pass_opcheck(native_lib):
     f_ids, f_lens, p_ids, p_lens, bits = _native.classify(mask, 128, 32)
     ex = lambda t, nd: t.expand(*((B, H) + tuple(t.shape[2:])))
     args = (q, k, v, mask.expand(B, H, S, S), bits, ex(f_ids, 4), ex(f_lens, 3), ex(p_ids, 4), ex(p_lens, 3),
-            128, 32, _native.SA_IMPL_AUTO, False)
+            128, 32, _native.SA_IMPL_AUTO, False, True)
     torch.library.opcheck(_native.attn_fwd_op, args, test_utils=checks)
 
 
@@ -293,3 +293,26 @@ def test_without_a_workspace_the_tiles_are_dealt_round_robin(native_lib, monkeyp
     monkeypatch.setattr(native_lib, "sa_attn_workspace_bytes", lambda: 0)
     without = _run(q, k, v, mask, 128, 32, impl="tcgen05")
     assert torch.equal(with_ws, without)
+
+
+@pytest.mark.parametrize("impl,dtype", [("tcgen05", torch.bfloat16), ("simt", torch.bfloat16), ("simt", torch.float32)])
+def test_lse_output(native_lib, impl, dtype):
+    """The optional log-sum-exp of a row's scaled scores over its attended keys (natural log), against
+    torch.logsumexp of the masked score matrix in fp32; -inf where a row attends to nothing."""
+    B, H, S, D = 1, 2, 512, 128
+    q, k, v = workloads.make_qkv(B, H, S, D, dtype, seed=51)
+    mask = workloads.random_block_mask(B, S, 0.5, 0.2, seed=52)
+    mask[:, :, 5, :] = False                                        # a row with no key
+    mask[:, :, 128:256, :] = False                                  # a whole query block with none
+    scores = torch.einsum("bhqd,bhkd->bhqk", q.float(), k.float()) * D ** -0.5
+    ref = torch.logsumexp(scores.masked_fill(~mask.expand(B, H, S, S), float("-inf")), dim=-1)
+    out, lse = sa.sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), 128, 32, impl=impl,
+                                   check_status=True, return_lse=True)
+    torch.cuda.synchronize()
+    lse = lse.cpu()
+    assert lse.shape == (B, H, S) and lse.dtype == torch.float32
+    empty = ~mask.expand(B, H, S, S).any(-1)
+    assert torch.isneginf(lse[empty]).all() and torch.isfinite(lse[~empty]).all()
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert (lse[~empty] - ref[~empty]).abs().max().item() <= tol
+    assert_close_attn(out, sdpa_cpu(q, k, v, mask), dtype, f"lse run {impl}")
