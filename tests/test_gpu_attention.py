@@ -8,7 +8,7 @@ import sparseattention_b200 as sa
 from oracle import attention as oa
 from oracle import classifier as oc
 from sparseattention_b200 import _native, workloads
-from _util import assert_close_attn, sdpa_cpu, MAX_ABS_16
+from _util import assert_close_attn, assert_lists_equal, sdpa_cpu, MAX_ABS_16
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -316,3 +316,26 @@ def test_lse_output(native_lib, impl, dtype):
     tol = 1e-4 if dtype == torch.float32 else 2e-2
     assert (lse[~empty] - ref[~empty]).abs().max().item() <= tol
     assert_close_attn(out, sdpa_cpu(q, k, v, mask), dtype, f"lse run {impl}")
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+@pytest.mark.parametrize("Sq,Sk", [(256, 1024), (1024, 384)])
+def test_rectangular_attention(native_lib, impl, Sq, Sk):
+    """Sq != Sk (cross attention / a decode chunk against a longer cache): the reference's kernels take the
+    two lengths separately (sparse_attn_kernel.py:150-151); lists, bit plane and tiles must too."""
+    B, H, D = 2, 3, 128
+    g = torch.Generator().manual_seed(Sq + Sk)
+    q = torch.randn((B, H, Sq, D), generator=g).to(torch.bfloat16)
+    k = torch.randn((B, H, Sk, D), generator=g).to(torch.bfloat16)
+    v = torch.randn((B, H, Sk, D), generator=g).to(torch.bfloat16)
+    blocks = torch.rand((B, 1, Sq // 32, Sk // 32), generator=g) < 0.5
+    mask = blocks.repeat_interleave(32, 2).repeat_interleave(32, 3)
+    noisy = torch.rand((B, 1, Sq, Sk), generator=g) < 0.5
+    part = (torch.rand((B, 1, Sq // 32, Sk // 32), generator=g) < 0.2).repeat_interleave(32, 2).repeat_interleave(32, 3)
+    mask = mask & (~part | noisy)
+    ref = sdpa_cpu(q, k, v, mask)
+    md = sa.compute_mask_kernel(mask.to(DEV).expand(B, H, Sq, Sk), 128, 32)
+    assert_lists_equal(md, oc.classify(mask.expand(B, H, Sq, Sk).numpy(), 128, 32), f"rectangular {Sq}x{Sk}")
+    out = _run(q, k, v, mask, 128, 32, impl=impl, md=md)
+    assert out.shape == (B, H, Sq, D)
+    assert_close_attn(out, ref, torch.bfloat16, f"rectangular {impl} {Sq}x{Sk}")
