@@ -339,3 +339,21 @@ def test_rectangular_attention(native_lib, impl, Sq, Sk):
     out = _run(q, k, v, mask, 128, 32, impl=impl, md=md)
     assert out.shape == (B, H, Sq, D)
     assert_close_attn(out, ref, torch.bfloat16, f"rectangular {impl} {Sq}x{Sk}")
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "simt"])
+def test_shared_key_value_heads(native_lib, impl):
+    """K and V given as views expanded over the heads (one kv head shared by all query heads, stride 0):
+    read in place, no copy; same values as with the heads materialised."""
+    B, H, S, D = 2, 4, 512, 128
+    g = torch.Generator().manual_seed(91)
+    q = torch.randn((B, H, S, D), generator=g).to(torch.bfloat16)
+    k1 = torch.randn((B, 1, S, D), generator=g).to(torch.bfloat16)
+    v1 = torch.randn((B, 1, S, D), generator=g).to(torch.bfloat16)
+    mask = workloads.random_block_mask(B, S, 0.4, 0.2, seed=92)
+    ref = sdpa_cpu(q, k1.expand(B, H, S, D).contiguous(), v1.expand(B, H, S, D).contiguous(), mask)
+    kd, vd = k1.to(DEV).expand(B, H, S, D), v1.to(DEV).expand(B, H, S, D)
+    assert kd.stride(1) == 0
+    out = sa.sparse_attention(q.to(DEV), kd, vd, mask.to(DEV), 128, 32, impl=impl, check_status=True)
+    torch.cuda.synchronize()
+    assert_close_attn(out, ref, torch.bfloat16, f"shared kv heads {impl}")
