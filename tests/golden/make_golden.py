@@ -1,9 +1,9 @@
 """Generates ``reference_vectors.npz``: inputs and the outputs of the REFERENCE itself.
 
-Run in a container that has the reference checkout (default ``/root/reference``) and
-triton installed; no GPU is needed:
+Run where a checkout of the reference (tomatillos/sparseattention) and triton are available; no GPU
+is needed:
 
-    python tests/golden/make_golden.py [--reference /path/to/sparseattention-checkout]
+    python tests/golden/make_golden.py --reference /path/to/sparseattention-checkout
 
 What it records, per case:
 
@@ -46,7 +46,7 @@ B, H, S, D = 1, 2, 256, 64
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import sparseattention.mask_utils as mu
