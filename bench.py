@@ -140,7 +140,7 @@ def cpu_sample(sample_heads: int, steps: int, warmup: int):
     import torch.nn.functional as F
 
     from oracle import cclassify
-    from sparseattention_b200 import workloads
+    import workloads
 
     cfg = workloads.CONFIGS["headline"]
     cores = os.cpu_count() or 1
@@ -198,7 +198,8 @@ def workload_name():
 
 def run_ours(args):
     import sparseattention_b200 as sa
-    from sparseattention_b200 import _native, workloads
+    import workloads
+    from sparseattention_b200 import _native
 
     rank, world, local = dist_env()
     if world != args.gpus and world > 1:

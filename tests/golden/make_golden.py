@@ -31,7 +31,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
-from sparseattention_b200 import workloads  # noqa: E402
+import workloads  # noqa: E402
 
 CASES = [
     # name, mask kind, BLOCK_Q, BLOCK_K

@@ -8,7 +8,8 @@ import torch
 import sparseattention_b200 as sa
 from oracle import cclassify
 from oracle import classifier as oc
-from sparseattention_b200 import _native, workloads
+import workloads
+from sparseattention_b200 import _native
 from _util import assert_lists_equal, oracle_lists
 
 pytestmark = pytest.mark.gpu

@@ -1,13 +1,14 @@
 """The document, composed and scaling configurations at their real sequence lengths (a few heads
 of one batch element): bit-exact lists against the C oracle, the tcgen05 kernel against the
-CUDA-core kernel over every row, and against host SDPA on one head where that is affordable."""
+CUDA-core kernel over every row, and against host SDPA on one head (S = 32768: on four query blocks
+of one head, over every key)."""
 import numpy as np
 import pytest
 import torch
 
 import sparseattention_b200 as sa
 from oracle import cclassify
-from sparseattention_b200 import workloads
+import workloads
 from _util import assert_close_attn, assert_lists_equal, sdpa_cpu, MAX_ABS_16, MEAN_ABS_16
 
 pytestmark = pytest.mark.gpu
@@ -28,6 +29,13 @@ def _check(mask, S, H, seed, sdpa_head=True, bk=32):
     if sdpa_head:
         want = sdpa_cpu(q[:, :1], k[:, :1], v[:, :1], mask)
         assert_close_attn(out[:, :1], want, torch.bfloat16, "vs SDPA")
+    else:
+        # host SDPA over every key for a few query blocks spread over the sequence (first, last, and two
+        # that straddle document boundaries somewhere in between)
+        for blk in (0, S // 128 // 3, 2 * (S // 128) // 3 + 1, S // 128 - 1):
+            rows = slice(128 * blk, 128 * (blk + 1))
+            want = sdpa_cpu(q[:, :1, rows], k[:, :1], v[:, :1], mask[:, :, rows])
+            assert_close_attn(out[:, :1, rows], want, torch.bfloat16, f"vs SDPA, query block {blk}")
     # skipped tiles really are empty: the listed tiles cover every True element
     tiles = int(md.unmasked_lens[0, 0].sum()) + int(md.masked_lens[0, 0].sum())
     return tiles / ((S // 128) * (S // bk))

@@ -1,0 +1,187 @@
+"""The online softmax of the tensor-core kernel on inputs whose row maximum is large and moves late.
+
+The kernel keeps, per query row, a reference value that only moves when a score exceeds it by more than
+2^8 (or when a fresh row's scores all lie far below 0); when it moves, the accumulated output is
+rescaled in tensor memory and the step is redone.  N(0,1) inputs never get there, so these cases build
+logits of tens of log2 units whose maximum rises several times along the walk over the two lists
+(sparse_attn_kernel.py:48-58 keeps the exact running maximum for any magnitude), and check every row
+against host SDPA.  Each case first counts, on the host, how often the walk makes the reference move at
+a step after the first, so that a test which stops reaching the path fails instead of passing idly.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import sparseattention_b200 as sa
+from oracle import classifier as oc
+from sparseattention_b200 import _native
+from _util import assert_close_attn, sdpa_cpu
+from workloads import random_block_mask  # repo root (tests/conftest.py puts it on sys.path)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+THRESHOLD = 8.0        # log2 units by which a score must exceed the reference before it moves
+FRESH_FLOOR = -4.0     # a fresh row whose largest score is below this takes that score as reference
+
+
+def _scale_log2(D):
+    return D ** -0.5 / math.log(2)
+
+
+def _walk_events(q, k, mask, bk):
+    """Follows the kernel's walk (full list, then partial list, 128 kv rows per step) for every query row
+    with the reference-moving rule above.  Returns (moves at steps > 0, moves through the fresh floor,
+    rows whose first attended key lies in a step > 0)."""
+    B, H, S, D = q.shape
+    lists = oc.classify(np.ascontiguousarray(mask.expand(B, H, S, S).numpy()), 128, bk)
+    s = torch.einsum("bhqd,bhkd->bhqk", q.float(), k.float()) * _scale_log2(D)
+    s = s.masked_fill(~mask.expand(B, H, S, S), float("-inf")).numpy()
+    per_step = 128 // bk
+    late, floor, late_first = 0, 0, 0
+    for b in range(B):
+        for h in range(H):
+            for i in range(S // 128):
+                ids = list(lists.unmasked_kv_ids[b, h, i, :lists.unmasked_lens[b, h, i]]) + \
+                      list(lists.masked_kv_ids[b, h, i, :lists.masked_lens[b, h, i]])
+                m = np.full(128, -np.inf, dtype=np.float32)
+                for j in range(0, len(ids), per_step):
+                    cols = np.concatenate([np.arange(c * bk, (c + 1) * bk) for c in ids[j:j + per_step]])
+                    x = s[b, h, 128 * i:128 * (i + 1)][:, cols].max(axis=1)
+                    fresh = np.isneginf(m)
+                    seen = ~np.isneginf(x)
+                    ref = np.where(fresh, 0.0, m)
+                    up = seen & (x - ref > THRESHOLD)
+                    down = fresh & seen & (x - ref < FRESH_FLOOR)
+                    if j > 0:
+                        late += int((up & ~fresh).sum())
+                        late_first += int((fresh & seen).sum())
+                    floor += int(down.sum())
+                    m = np.where(up | down, x, np.where(seen & fresh, 0.0, m)).astype(np.float32)
+    return late, floor, late_first
+
+
+def _lse_ref(q, k, mask):
+    B, H, S, D = q.shape
+    s = torch.einsum("bhqd,bhkd->bhqk", q.float(), k.float()) * D ** -0.5
+    return torch.logsumexp(s.masked_fill(~mask.expand(B, H, S, S), float("-inf")), dim=-1)
+
+
+def _check(q, k, v, mask, bk, dtype, what):
+    ref = sdpa_cpu(q, k, v, mask)
+    out, lse = sa.sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), 128, bk, impl="tcgen05",
+                                   check_status=True, return_lse=True)
+    torch.cuda.synchronize()
+    assert_close_attn(out, ref, dtype, what)
+    want = _lse_ref(q, k, mask)
+    have = lse.cpu()
+    live = torch.isfinite(want)
+    assert torch.isneginf(have[~live]).all(), what
+    # log-sum-exp of logits of tens of nats: absolute 2e-2 on values up to ~60
+    assert (have[live] - want[live]).abs().max().item() <= 2e-2, what
+    # the CUDA-core kernel keeps the exact running maximum: a second opinion on the same lists
+    simt = sa.sparse_attention(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), 128, bk, impl="simt",
+                               check_status=True)
+    assert_close_attn(simt, ref, dtype, what + " (generic kernel)")
+
+
+def _planted_inputs(B, H, S, D, dtype, seed, drop_p):
+    """Q four times wider than N(0,1); K rows growing with the key position; on top, for a sixth of the
+    query rows, three planted keys each (in three different 128-key regions, ascending) whose scores are
+    32, 48 and 64 log2 units, attended through the mask whatever block they fall in (so they land in full
+    blocks, partial blocks and in blocks that were dropped and now hold a single True)."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn((B, H, S, D), generator=g) * 4.0
+    k = torch.randn((B, H, S, D), generator=g)
+    v = torch.randn((B, H, S, D), generator=g)
+    growth = 1.0 + 0.6 * (torch.arange(S) // 128).float()
+    k = k * growth[None, None, :, None]
+    mask = random_block_mask(B, S, drop_p, 0.25, seed=seed)
+    q = q.to(dtype).float()                      # the planted keys are built from the rounded queries
+    sl2 = _scale_log2(D)
+    n_regions = S // 128
+    for b in range(B):
+        for r in range(int(torch.randint(0, 6, (1,), generator=g)), S, 6):
+            regions = torch.randperm(n_regions, generator=g)[:3].sort().values.tolist()
+            for t, reg in enumerate(regions):
+                kpos = reg * 128 + int(torch.randint(0, 128, (1,), generator=g))
+                target = 32.0 + 16.0 * t
+                for h in range(H):
+                    qr = q[b, h, r]
+                    k[b, h, kpos] = qr * (target / (sl2 * float(qr @ qr)))
+                mask[b, 0, r, kpos] = True
+    return q.to(dtype), k.to(dtype), v.to(dtype), mask
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,bk", [(128, 32), (128, 64), (128, 128), (64, 32), (64, 128)])
+def test_reference_moves_late_and_often(native_lib, dtype, D, bk):
+    B, H, S = 2, 2, 1024
+    q, k, v, mask = _planted_inputs(B, H, S, D, dtype, seed=1000 + D + bk, drop_p=0.4)
+    late, _, _ = _walk_events(q, k, mask, bk)
+    assert late > 500, f"only {late} late moves: the inputs no longer reach the rescale path"
+    _check(q, k, v, mask, bk, dtype, f"late maxima {dtype} D={D} bk={bk}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_reference_moves_in_the_ragged_last_step(native_lib, dtype):
+    """Lists of 1..7 blocks per query block (ragged 128-row steps, padding slots), every block partial,
+    keys growing fast enough that the last, padded step moves the reference of most rows."""
+    B, H, S, D, bk = 1, 2, 1024, 128, 32
+    g = torch.Generator().manual_seed(77)
+    q = (torch.randn((B, H, S, D), generator=g) * 4.0).to(dtype)
+    k = torch.randn((B, H, S, D), generator=g)
+    v = torch.randn((B, H, S, D), generator=g).to(dtype)
+    k = (k * (1.0 + 1.5 * (torch.arange(S) // 32).float() / 8.0)[None, None, :, None]).to(dtype)
+    mask = torch.zeros((B, 1, S, S), dtype=torch.bool)
+    for i in range(8):
+        cols = torch.randperm(32, generator=g)[: i + 1].sort().values.tolist()
+        for n, c in enumerate(cols):
+            tile = torch.rand((128, 32), generator=g) < 0.6
+            if n < (i + 1) // 3:
+                tile[:] = True
+            mask[0, 0, 128 * i:128 * (i + 1), 32 * c:32 * c + 32] = tile
+    late, _, _ = _walk_events(q, k, mask, bk)
+    assert late > 100, late
+    _check(q, k, v, mask, bk, dtype, f"ragged last step {dtype}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D,bk", [(128, 32), (64, 128)])
+def test_all_scores_far_below_zero_and_late_first_key(native_lib, dtype, D, bk):
+    """Every score is about -20 log2 units (a fresh row's first scores are tried against 0, which would
+    flush P to nothing): the reference has to drop to the row's own maximum.  Some rows attend to nothing
+    in the first steps of their walk and meet their first key later."""
+    B, H, S = 1, 2, 1024
+    g = torch.Generator().manual_seed(5 + D + bk)
+    q = torch.randn((B, H, S, D), generator=g)
+    k = torch.randn((B, H, S, D), generator=g)
+    v = torch.randn((B, H, S, D), generator=g).to(dtype)
+    c = math.sqrt(20.0 / _scale_log2(D))
+    q[..., 0] = c
+    k[..., 0] = -c
+    q, k = q.to(dtype), k.to(dtype)
+    mask = random_block_mask(B, S, 0.3, 0.2, seed=11 + bk)
+    mask[0, 0, 3::8, :384] = False              # rows whose first attended key comes after three steps' worth of keys
+    mask[0, 0, 133, :] = False
+    mask[0, 0, 133, 1000] = True                # a row with a single, late key
+    _, floor, late_first = _walk_events(q, k, mask, bk)
+    assert floor > 1000 and late_first > 50, (floor, late_first)
+    _check(q, k, v, mask, bk, dtype, f"low scores {dtype} D={D} bk={bk}")
+
+
+def test_mixed_magnitudes_dense(native_lib):
+    """No mask at all (every step is a step of full blocks): rows with small logits next to rows whose
+    maximum rises by more than the threshold at every step."""
+    B, H, S, D, bk = 1, 2, 2048, 128, 128
+    g = torch.Generator().manual_seed(99)
+    q = torch.randn((B, H, S, D), generator=g)
+    q[:, :, 1::2] *= 6.0                        # odd rows: wide logits; even rows: N(0,1) logits
+    k = torch.randn((B, H, S, D), generator=g) * (1.0 + 0.5 * (torch.arange(S) // 128).float())[None, None, :, None]
+    v = torch.randn((B, H, S, D), generator=g)
+    q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    mask = torch.ones((1, 1, S, S), dtype=torch.bool)
+    late, _, _ = _walk_events(q, k, mask, bk)
+    assert late > 2000, late
+    _check(q, k, v, mask, bk, torch.bfloat16, "dense, mixed magnitudes")

@@ -9,7 +9,8 @@ import pytest
 import torch
 
 from oracle import classifier as oc
-from sparseattention_b200 import _native, workloads
+import workloads
+from sparseattention_b200 import _native
 import sparseattention_b200 as sa
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

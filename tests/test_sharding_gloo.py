@@ -9,7 +9,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 import torch.nn.functional as F
 
-from sparseattention_b200 import sharding, workloads
+import workloads
+from sparseattention_b200 import sharding
 
 
 def test_partition_covers_every_unit_once():

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from sparseattention_b200 import workloads
+import workloads
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
