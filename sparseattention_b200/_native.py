@@ -125,7 +125,7 @@ def _canonical_mask(mask: torch.Tensor) -> torch.Tensor:
     return base
 
 
-@torch.library.custom_op("sparseattention_b200::classify_mask", mutates_args=())
+@torch.library.custom_op("sparseattention::classify_mask", mutates_args=())
 def classify_mask_op(mask: torch.Tensor, block_q: int, block_k: int,
                      with_bits: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """mask: bool [Bu,Hu,Sq,Sk] holding only the distinct planes.  Returns
@@ -207,7 +207,7 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
-@torch.library.custom_op("sparseattention_b200::attn_fwd", mutates_args=())
+@torch.library.custom_op("sparseattention::attn_fwd", mutates_args=())
 def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, bits: torch.Tensor,
                 full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
                 block_q: int, block_k: int, impl: int, check_status: bool,

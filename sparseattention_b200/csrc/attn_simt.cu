@@ -4,8 +4,8 @@
 // per query block, loop A over the full list without the mask, loop B over the partial
 // list with the boolean mask applied as -inf, online softmax in base 2 with fp32 running
 // max / sum / accumulator, P rounded to the V dtype before P.V (line 61), O = acc / l.
-// It takes any dtype (fp32 / fp16 / bf16), any strides (0 included), head dims that are
-// multiples of 4 up to 256 and block sizes that are multiples of 32, reads the byte mask
+// It takes any dtype (fp32 / fp16 / bf16), any strides (0 included), head dims 16, 32, 64
+// and 128 and block sizes that are multiples of 32, reads the byte mask
 // directly, and is the path for shapes the tcgen05 kernel does not cover.  Rows without
 // any attended key come out as 0.
 //
@@ -42,8 +42,9 @@ attn_simt_kernel(const AttnParams p) {
 
   const int tid = threadIdx.x;
   const int r = tid >> 2, ql = tid & 3;
-  const int row = blockIdx.x * kRows + r;
-  const int bh = blockIdx.y;
+  const int row_groups = p.Sq / kRows;                   // 1-D grid: (batch * head, group of 32 query rows)
+  const int row = static_cast<int>(blockIdx.x % row_groups) * kRows + r;
+  const int bh = static_cast<int>(blockIdx.x / row_groups);
   const int b = bh / p.H, h = bh % p.H;
   const int qblk = row / p.BQ;
   const int nk = p.Sk / p.BK;
@@ -68,9 +69,13 @@ attn_simt_kernel(const AttnParams p) {
         ? p.part_ids + b * p.pis[0] + h * p.pis[1] + static_cast<int64_t>(qblk) * p.pis[2]
         : p.full_ids + b * p.fis[0] + h * p.fis[1] + static_cast<int64_t>(qblk) * p.fis[2];
     const int64_t id_stride = masked ? p.pis[3] : p.fis[3];
-    const int n = masked
+    const int n_given = masked
         ? p.part_lens[b * p.pls[0] + h * p.pls[1] + static_cast<int64_t>(qblk) * p.pls[2]]   // line 127
         : p.full_lens[b * p.fls[0] + h * p.fls[1] + static_cast<int64_t>(qblk) * p.fls[2]];  // line 107
+    // A caller-supplied length outside [0, nk] would walk the id list out of bounds: it is clamped
+    // (as the tensor-core kernel does) and reported.
+    const int n = min(max(n_given, 0), nk);
+    if (n != n_given && tid == 0 && p.dev_status != nullptr) atomicMax(p.dev_status, SA_DEV_BAD_INDEX);
 #pragma unroll 1
     for (int t = 0; t < n; ++t) {
       const int id = ids[t * id_stride];                                 // line 33
@@ -136,7 +141,9 @@ attn_simt_kernel(const AttnParams p) {
 
 template <typename T>
 cudaError_t launch_for_dtype(const AttnParams& p, cudaStream_t stream) {
-  dim3 grid(p.Sq / kRows, p.B * p.H);
+  const long long ctas = static_cast<long long>(p.Sq / kRows) * p.B * p.H;
+  if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  dim3 grid(static_cast<unsigned>(ctas));
   switch (p.D) {
     case 16:  attn_simt_kernel<T, 16><<<grid, kThreads, 0, stream>>>(p); break;
     case 32:  attn_simt_kernel<T, 32><<<grid, kThreads, 0, stream>>>(p); break;

@@ -108,3 +108,17 @@ def test_flop_accounting():
     assert workloads.computed_tile_flops(lens, lens, 128, 32, 128) == 4 * 128 * 128 * 32 * 8
     assert workloads.dense_flops(8, 32, 4096, 4096, 128) == pytest.approx(2.199e12, rel=1e-3)
     assert workloads.classifier_bytes(8, 4096, 4096, 128, 0) == 8 * 4096 * 4096 + 8 * 8 * 32
+
+
+def test_reference_module_names_resolve_to_this_library():
+    """``sparseattention.mask_utils`` / ``sparseattention.sparse_attn_kernel`` (the reference's module
+    paths) export the reference's names, backed by this package; the torch ops carry the package name."""
+    import sparseattention.mask_utils as mu
+    import sparseattention.sparse_attn_kernel as sak
+    import sparseattention_b200 as impl
+    assert mu.MaskMetadata is impl.MaskMetadata and mu.compute_mask_kernel is impl.compute_mask_kernel
+    assert mu.compute_mask_slow is impl.compute_mask_slow and sak.sparse_attention is impl.sparse_attention
+    assert sak.compute_mask_kernel is impl.compute_mask_kernel
+    assert hasattr(torch.ops.sparseattention, "classify_mask") and hasattr(torch.ops.sparseattention, "attn_fwd")
+    with pytest.raises(RuntimeError):           # CUDA tensors only: no CPU implementation is registered
+        mu.compute_mask_kernel(torch.ones((1, 1, 128, 128), dtype=torch.bool), 128, 32)
