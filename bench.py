@@ -16,6 +16,13 @@ divided by the time of both stages.  ``value`` is measured with all inputs resid
 HBM; ``e2e`` goes through the public Python entry points with host (pinned) inputs, the
 host->device and device->host copies inside the timed region.
 
+Beside the metric the line carries: ``sharded`` -- the multi-GPU configuration (B=16, H=32,
+S=32768, document masks) cut over the ranks by (batch, head) with every rank classifying only
+its own mask planes (strong scaling; per-rank stage times, imbalance, a gather check);
+``comparators`` -- torch SDPA, FlexAttention and the reference's own Triton kernels on the same
+GPU and inputs (N = 1); ``attention_results`` -- the per-p records in the layout of the reference
+harness's ``attention_results.json`` (test_attn.py:91-128).
+
 ``--impl reference`` times the reference's CPU path for the same metric on the host
 cores: the C restatement of its classifier plus torch SDPA with the bool mask (its own
 ground truth, test_attn.py:40) on a bounded sample of the workload.
@@ -41,6 +48,7 @@ METRIC = "effective_tflops_attn_plus_mask_preprocess"
 UNIT = "TFLOP/s"
 BQ, BK = 128, 32
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0}
 
 
 def load_peaks():
@@ -99,15 +107,7 @@ class ClockSampler:
     def start(self):
         try:
             import pynvml
-            pynvml.nvmlInit()
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            idx = self.index
-            if visible:
-                try:
-                    idx = int(visible.split(",")[self.index])
-                except ValueError:
-                    pass
-            handle = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            handle = nvml_handle(self.index)
             self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
             self.source = "nvml"
             self.thread = threading.Thread(target=self._nvml_loop, args=(pynvml, handle), daemon=True)
@@ -122,6 +122,45 @@ class ClockSampler:
             self.thread.join(timeout=10)
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.sm_max,
                 "samples": len(self.samples), "reasons": sorted(self.reasons), "source": self.source}
+
+
+def nvml_handle(local_index: int):
+    """NVML handle of the CUDA device ``local_index`` of this process (read-only use)."""
+    import pynvml
+    pynvml.nvmlInit()
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    idx = local_index
+    if visible:
+        try:
+            idx = int(visible.split(",")[local_index])
+        except ValueError:
+            pass
+    return pynvml.nvmlDeviceGetHandleByIndex(idx)
+
+
+def bind_to_gpu_cpus(local_index: int):
+    """Restricts this process to the host CPUs NVML names as local to its GPU (same NUMA node / PCIe root),
+    intersected with what the process may use, so that the pinned buffers allocated afterwards are placed
+    and touched next to the GPU.  Returns a small record for the JSON line; changes nothing on the GPU."""
+    rec = {"bound": False}
+    try:
+        import pynvml
+        handle = nvml_handle(local_index)
+        allowed = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (max(allowed | {os.cpu_count() or 1}) // 64) + 1)
+        local = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        both = allowed & local
+        rec.update({"gpu_local_cpus": len(local), "allowed_cpus": len(allowed), "usable_local_cpus": len(both)})
+        if both and both != allowed:
+            os.sched_setaffinity(0, both)
+            rec["bound"] = True
+        elif both == allowed:
+            rec["note"] = "every allowed CPU is already local to the GPU"
+        else:
+            rec["note"] = "no allowed CPU is local to the GPU; affinity left as it was"
+    except Exception as e:                       # no NVML, or a container that hides the topology
+        rec["note"] = f"not bound: {type(e).__name__}: {e}"[:160]
+    return rec
 
 
 def dist_env():
@@ -139,8 +178,8 @@ def cpu_sample(sample_heads: int, steps: int, warmup: int):
     import numpy as np
     import torch.nn.functional as F
 
-    from oracle import cclassify
     import workloads
+    from oracle import cclassify
 
     cfg = workloads.CONFIGS["headline"]
     cores = os.cpu_count() or 1
@@ -174,8 +213,8 @@ def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    warm = max(1, min(args.warmup, 1))
+    steps = max(1, min(args.steps, 20))          # a step of the sample takes ~70 ms: 20 + 5 stay within seconds
+    warm = max(1, min(args.warmup, 5))
     val, sec, desc, cores = cpu_sample(args.cpu_heads, steps, warm)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
@@ -194,6 +233,162 @@ def workload_name():
             "{0,0.1,0.3,0.5,0.7,0.9}, 10% of kept blocks Bernoulli(0.5), BLOCK_Q=128 BLOCK_K=32, per GPU")
 
 
+# ------------------------------------------------------------------------------- helpers
+
+def best_ms(fn, n=5, warm=2):
+    """Best of ``n`` CUDA-event timings of ``fn()`` on the current stream, after ``warm`` untimed runs."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(n):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return min(ts)
+
+
+def barrier(world):
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------------------- sharded configuration
+
+def document_costs(cfg, batch, seed_base):
+    """Per batch element, the sum over its documents of len^2 / 2 -- what a causal document mask
+    attends to, known from the (host-side, seeded) document lengths before any mask exists."""
+    import workloads
+    costs = []
+    for b in range(batch):
+        lens = workloads.document_lengths(cfg.S, cfg.doc_len[0], cfg.doc_len[1], workloads._cpu_gen(seed_base + b))
+        costs.append(sum(0.5 * n * n for n in lens))
+    return costs
+
+
+def run_sharded(rank, world, dev, steps, warmup, balance=True, batch=0, seq=0):
+    """The multi-GPU configuration -- B=16, H=32, S=32768, D=128, bf16, per-batch document + causal masks
+    with 5 % of the kept 32x32 blocks internally Bernoulli(0.5) -- cut over the ranks by (batch, head):
+    strong scaling, no collective on the data path.  Every rank builds, holds and classifies only the mask
+    planes of its own batch elements and runs both stages through ``sharding.run_slabs``.  Returns the
+    ``sharded`` record (rank 0) or None."""
+    import sparseattention_b200 as sa
+    import workloads
+    from oracle import attention as oa
+    from sparseattention_b200 import sharding
+
+    cfg = workloads.CONFIGS["scaling"]
+    B, H, S, D = (batch or cfg.B), cfg.H, (seq or cfg.S), cfg.D
+    seed_mask, seed_qkv = 5000, 6000
+    if seq:
+        cfg = workloads.WorkloadConfig(cfg.name, B, H, S, D, cfg.dtype, cfg.kind, cfg.drop_ps, cfg.partial_frac,
+                                       (min(cfg.doc_len[0], S // 8), min(cfg.doc_len[1], S // 2)))
+    costs = document_costs(cfg, B, seed_mask)
+    slabs = sharding.slabs_of(B, H, rank, world, costs if balance else None)
+    store = {}
+    for slab in slabs:                                        # this rank's data only
+        mask = workloads.document_causal_mask(1, S, cfg.doc_len, cfg.partial_frac, seed=seed_mask + slab.b, device=dev)
+        q, k, v = workloads.make_qkv(1, H, S, D, torch.bfloat16, seed=seed_qkv + slab.b, device=dev)
+        sl = slice(slab.h0, slab.h1)
+        store[slab] = (q[:, sl].contiguous(), k[:, sl].contiguous(), v[:, sl].contiguous(), mask)
+        del q, k, v
+    fetch = store.__getitem__
+
+    # untimed pass: FLOPs of the listed tiles, device status, and a host check of one query block per slab
+    flops = 0.0
+    err_max, err_mean = 0.0, 0.0
+    for slab in slabs:
+        q, k, v, mask = store[slab]
+        h = q.shape[1]
+        md = sa.compute_mask_kernel(mask.expand(1, h, S, S), BQ, BK)
+        flops += workloads.computed_tile_flops(md.unmasked_lens, md.masked_lens, BQ, BK, D)
+        o = sa.sparse_attention(q, k, v, mask, BQ, BK, mask_metadata=md, impl="tcgen05", check_status=True)
+        blk = min(S // BQ - 1, (S // BQ) * 2 // 3 + slab.b % 7)   # past the middle, different per batch element
+        rows = slice(BQ * blk, BQ * (blk + 1))
+        want = torch.from_numpy(oa.sdpa_reference(q[:, :1, rows], k[:, :1], v[:, :1], mask[:, :, rows]))
+        d = (o[:, :1, rows].float().cpu() - want).abs()
+        err_max, err_mean = max(err_max, d.max().item()), max(err_mean, d.mean().item())
+        del o, md
+
+    def attend(q, k, v, m, bq, bk, mask_metadata=None):
+        return sa.sparse_attention(q, k, v, m, bq, bk, mask_metadata=mask_metadata, impl="tcgen05")
+
+    for _ in range(warmup):
+        sharding.run_slabs(slabs, fetch, BQ, BK, attention=attend)
+    barrier(world)
+    events_all = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        ev = []
+        sharding.run_slabs(slabs, fetch, BQ, BK, attention=attend, events=ev)
+        events_all.append(ev)
+    t1.record()
+    barrier(world)
+    my_ms = t0.elapsed_time(t1) / steps
+    cls_ms = statistics.mean(sum(e[0].elapsed_time(e[1]) for _, e in ev) for ev in events_all) if slabs else 0.0
+    att_ms = statistics.mean(sum(e[1].elapsed_time(e[2]) for _, e in ev) for ev in events_all) if slabs else 0.0
+    store.clear()
+    torch.cuda.empty_cache()
+
+    # gather check on a reduced problem: every rank runs its share of globally indexed inputs through
+    # sharded_forward, the outputs are assembled with one all_gather (NCCL) and compared, bit for bit,
+    # with the unsharded call on this GPU
+    vB, vH, vS = 4, 8, 2048
+    vq, vk, vv = workloads.make_qkv(vB, vH, vS, D, torch.bfloat16, seed=77, device=dev)
+    vmask = workloads.document_causal_mask(vB, vS, (200, 900), 0.05, seed=78, device=dev)
+    vcosts = [float(x) for x in range(1, vB + 1)]
+    whole = sa.sparse_attention(vq, vk, vv, vmask, BQ, BK)
+    local = sharding.sharded_forward(vq, vk, vv, vmask, BQ, BK, rank, world, costs=vcosts)
+    if world > 1:
+        full = sharding.gather_outputs(local, vB, vH, device=dev, costs=vcosts)
+    else:
+        full = torch.empty_like(whole)
+        for slab, o in local:
+            full[slab.b, slab.h0:slab.h1] = o[0]
+    gather_ok = bool(torch.equal(full, whole))
+
+    rec = {"rank": rank, "units": sum(s.h1 - s.h0 for s in slabs), "classify_ms": cls_ms, "attn_ms": att_ms,
+           "ms_per_step": my_ms, "flops_per_step": flops, "err_max_vs_sdpa": err_max, "err_mean_vs_sdpa": err_mean,
+           "gather_bit_exact": gather_ok}
+    if world > 1:
+        recs = [None] * world
+        torch.distributed.all_gather_object(recs, rec)
+    else:
+        recs = [rec]
+    if rank != 0:
+        return None
+    ms = [r["ms_per_step"] for r in recs]
+    total_flops = sum(r["flops_per_step"] for r in recs)
+    peaks, _ = load_peaks()
+    return {
+        "workload": f"scaling: B={B} H={H} S={S} D={D} bf16, per-batch document+causal masks (lengths U[{cfg.doc_len[0]},"
+                    f"{cfg.doc_len[1]}], {int(cfg.partial_frac * 100)}% of kept 32x32 blocks Bernoulli(0.5)), "
+                    f"BLOCK_Q={BQ} BLOCK_K={BK}; (batch, head) units cut over the ranks, each rank classifies its own mask planes",
+        "scaling": "strong", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "partition": "contiguous (batch, head) ranges with equal summed cost (sum of squared document lengths)"
+                     if balance else "contiguous (batch, head) ranges with equal unit counts",
+        "ms_per_step_max_over_ranks": max(ms), "ms_per_step_mean_over_ranks": statistics.mean(ms),
+        "imbalance_max_over_mean": max(ms) / statistics.mean(ms),
+        "effective_tflops": total_flops / (max(ms) * 1e-3) / 1e12,
+        "frac_of_sustained_bf16_per_gpu": total_flops / (max(ms) * 1e-3) / 1e12 / world / peaks["bf16_tflops_sustained"],
+        "per_rank": [{"rank": r["rank"], "units": r["units"], "classify_ms": r["classify_ms"], "attn_ms": r["attn_ms"],
+                      "ms_per_step": r["ms_per_step"],
+                      "attn_tflops": r["flops_per_step"] / (r["attn_ms"] * 1e-3) / 1e12 if r["attn_ms"] > 0 else None}
+                     for r in recs],
+        "verification": {"gather_bit_exact_all_ranks": all(r["gather_bit_exact"] for r in recs),
+                         "gather_problem": f"B={vB} H={vH} S={vS}, cost-balanced cuts, all_gather over "
+                                           f"{'NCCL' if world > 1 else 'one rank (no collective)'}",
+                         "max_abs_err_vs_sdpa": max(r["err_max_vs_sdpa"] for r in recs),
+                         "mean_abs_err_vs_sdpa": max(r["err_mean_vs_sdpa"] for r in recs),
+                         "sdpa_rows": "one 128-row query block of one head per slab, every key, host SDPA"},
+    }
+
+
 # ------------------------------------------------------------------------------- GPU arm
 
 def run_ours(args):
@@ -204,6 +399,7 @@ def run_ours(args):
     rank, world, local = dist_env()
     if world != args.gpus and world > 1:
         args.gpus = world
+    numa = bind_to_gpu_cpus(local)                 # before any pinned allocation
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -229,15 +425,17 @@ def run_ours(args):
         return sa.sparse_attention(q, k, v, masks[i], BQ, BK, mask_metadata=md, impl="tcgen05")
 
     # one untimed pass: FLOP / byte accounting and a device-status check
-    flops_p, bytes_p, mix = [], [], []
+    flops_p, bytes_p, bits_bytes_p, mix, frac_unmasked = [], [], [], [], []
     for i in range(len(ps)):
         md = stage1(i)
         o = sa.sparse_attention(q, k, v, masks[i], BQ, BK, mask_metadata=md, impl="tcgen05", check_status=True)
         flops_p.append(workloads.computed_tile_flops(md.unmasked_lens, md.masked_lens, BQ, BK, D))
         lens_sum = int(md.unmasked_lens[:, 0].sum()) + int(md.masked_lens[:, 0].sum())
         bytes_p.append(workloads.classifier_bytes(planes, S, S, BQ, lens_sum))
+        bits_bytes_p.append(float(planes) * S * S / 8.0)        # the packed plane stage 2 reads (written by stage 1)
         tiles = B * H * (S // BQ) * (S // BK)
         mix.append((float(md.unmasked_lens.sum()) / tiles, float(md.masked_lens.sum()) / tiles))
+        frac_unmasked.append(float(masks[i].sum(dtype=torch.int64)) / masks[i].numel())
         del o, md
     flops_step = sum(flops_p)
 
@@ -256,31 +454,25 @@ def run_ours(args):
                 events[2 * i + 2].record()
         return o
 
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
     for _ in range(warmup):
         step()
-    barrier()
+    barrier(world)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    barrier(world)
     t_start.record()
     for s in range(args.steps):
         step(ev[s])
     t_end.record()
-    barrier()
+    barrier(world)
     clocks = sampler.stop() if rank == 0 else None
     elapsed_ms = t_start.elapsed_time(t_end)
 
     cls_ms = [statistics.mean(ev[s][2 * i].elapsed_time(ev[s][2 * i + 1]) for s in range(args.steps)) for i in range(n_p)]
     att_ms = [statistics.mean(ev[s][2 * i + 1].elapsed_time(ev[s][2 * i + 2]) for s in range(args.steps)) for i in range(n_p)]
 
-    # ---- end to end through the public entry points with host buffers
     if args.profile or args.workload != "headline":
         if world > 1:
             torch.distributed.destroy_process_group()
@@ -292,6 +484,20 @@ def run_ours(args):
                               "tile_mix_full_partial": mix,
                               "effective_tflops_both_stages": flops_step / (elapsed_ms / args.steps * 1e-3) / 1e12}))
         return
+
+    # ---- the caller's other list granularities on the p = 0.5 mask (stage 2 alone, lists passed in)
+    granularities = []
+    if 0.5 in ps:
+        i5 = ps.index(0.5)
+        for bq in (128, 64, 32):
+            md = sa.compute_mask_kernel(masks_e[i5], bq, BK)
+            t = best_ms(lambda: sa.sparse_attention(q, k, v, masks[i5], bq, BK, mask_metadata=md), n=5, warm=2)
+            listed = float(md.unmasked_lens.sum(dtype=torch.int64) + md.masked_lens.sum(dtype=torch.int64))
+            granularities.append({"BLOCK_Q": bq, "BLOCK_K": BK, "attn_ms": t,
+                                  "listed_tile_fraction": listed / (B * H * (S // bq) * (S // BK))})
+            del md
+
+    # ---- end to end through the public entry points with host buffers
     host_q, host_k, host_v = (t.cpu().pin_memory() for t in (q, k, v))
     host_masks = [m.cpu().pin_memory() for m in masks]
     host_o = torch.empty((B, H, S, D), dtype=dtype).pin_memory()
@@ -302,8 +508,9 @@ def run_ours(args):
     # copies; the copies of one mask overlap the kernels of the previous one (PCIe is full duplex).
     main = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dummy_o = torch.empty((B, H, S, D), dtype=dtype, device=dev)
 
-    def e2e_step():
+    def e2e_step(compute=True):
         # steps are pipelined too: the inputs of a step travel while the results of the previous one
         # are still going back (fresh device buffers per step; the caching allocator tracks the streams)
         with torch.cuda.stream(s_in):
@@ -318,7 +525,8 @@ def run_ours(args):
             t.record_stream(main)
         for i in range(n_p):
             main.wait_event(ready[i])
-            o = sa.sparse_attention(dq, dk, dv, dms[i], BQ, BK)  # the reference's call, stage 1 inside
+            # the reference's call, stage 1 inside; the copy-only run sends back a buffer of the same size
+            o = sa.sparse_attention(dq, dk, dv, dms[i], BQ, BK) if compute else dummy_o
             done = torch.cuda.Event()
             done.record(main)
             o.record_stream(s_out)
@@ -330,33 +538,54 @@ def run_ours(args):
         main.wait_stream(s_in)
         main.wait_stream(s_out)                                  # the last result is on the host
 
+    def e2e_time(n_steps, compute):
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        e2e_step(compute)
+        e2e_drain()
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        for _ in range(n_steps):
+            e2e_step(compute)
+        e2e_drain()
+        e1.record()
+        barrier(world)
+        return e0.elapsed_time(e1)
+
     e2e_steps = max(1, min(args.steps, 5))
-    s_in.wait_stream(main)
-    s_out.wait_stream(main)
-    e2e_step()
-    e2e_drain()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    s_in.wait_stream(main)
-    s_out.wait_stream(main)
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2e_drain()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    e2e_ms = e2e_time(e2e_steps, True)
+    copy_ms = e2e_time(e2e_steps, False)           # same buffers, streams and events, no kernels
+    del host_q, host_k, host_v, host_masks, host_o, dummy_o
 
     if world > 1:
         import torch.distributed as dist
-        t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([elapsed_ms, e2e_ms, copy_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = float(t[0]), float(t[1])
+        elapsed_ms, e2e_ms, copy_ms = float(t[0]), float(t[1]), float(t[2])
         f = torch.tensor([flops_step], device=dev, dtype=torch.float64)
         dist.all_reduce(f, op=dist.ReduceOp.SUM)
         flops_all = float(f[0])
     else:
         flops_all = flops_step
+
+    # ---- same-GPU comparators (N = 1; outside every timed region of the metric)
+    comparators = None
+    if world == 1 and not args.no_comparators:
+        comparators = gpu_comparators(q, k, v, masks, ps, flops_p)
+    del q, k, v, masks, masks_e
+    torch.cuda.empty_cache()
+
+    # ---- the sharded multi-GPU configuration (strong scaling), every rank
+    sharded = None
+    if not args.no_sharded:
+        try:
+            sharded = run_sharded(rank, world, dev, max(1, min(args.steps, 5)), 2)
+        except torch.cuda.OutOfMemoryError as e:
+            sharded = {"unavailable": f"out of device memory: {e}"[:200]} if rank == 0 else None
+        torch.cuda.empty_cache()
 
     if rank == 0:
         peaks, peak_kind = load_peaks()
@@ -366,6 +595,7 @@ def run_ours(args):
         att_tflops = flops_step / (att_total_ms * 1e-3) / 1e12
         cls_total_ms = sum(cls_ms)
         cls_gbs = sum(bytes_p) / (cls_total_ms * 1e-3) / 1e9
+        cls_gbs_with_plane = (sum(bytes_p) + sum(bits_bytes_p)) / (cls_total_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -375,24 +605,44 @@ def run_ours(args):
                        "shard": "each rank owns a full (batch, head) shard of the workload"},
             "roofline": {"bound": "tensor", "achieved": att_tflops, "peak": peaks["bf16_tflops_sustained"],
                          "unit": "TFLOP/s", "frac": att_tflops / peaks["bf16_tflops_sustained"],
+                         "frac_of_burst": att_tflops / peaks["bf16_tflops"],
+                         "frac_of_nominal": att_tflops / NOMINAL["bf16_tflops"],
                          "traffic": 254.3e6 * B / 2.0, "traffic_unit": "bytes per launch (ncu capture at B=2, p=0.5, scaled by batch)",
                          "kernel": "attn_fwd_tc_kernel<bf16,128>", "peak_source": peak_kind + " (sustained bf16 matmul)",
                          "note": "FLOPs of the listed tiles of all six launches / sum of their durations (CUDA events)"},
             "roofline_classifier": {"bound": "hbm", "achieved": cls_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                    "frac": cls_gbs / peaks["hbm_gbs"], "traffic": 276.7e6 * B / 16.0,
-                                    "traffic_unit": "bytes per launch (ncu capture at 16 planes, scaled by planes)",
-                                    "kernel": "classify_cells_kernel + compact_lists_kernel",
-                                    "note": "algorithmic bytes / duration of the whole stage-1 call incl. its allocations"},
+                                    "frac": cls_gbs / peaks["hbm_gbs"],
+                                    "frac_of_nominal": cls_gbs / NOMINAL["hbm_gbs"],
+                                    "achieved_with_packed_plane": cls_gbs_with_plane,
+                                    "frac_with_packed_plane": cls_gbs_with_plane / peaks["hbm_gbs"],
+                                    "traffic": None, "kernel": "classify_kernel",
+                                    "note": "algorithmic bytes (mask read once + lists; the 12.5 % of packed-plane writes "
+                                            "are counted only in the *_with_packed_plane figures) / duration of the whole "
+                                            "stage-1 call incl. its allocations"},
             "sweep": [{"p": p, "classify_ms": c, "attn_ms": a, "attn_tflops": fl / (a * 1e-3) / 1e12,
                        "classify_gbs": by / (c * 1e-3) / 1e9, "full_frac": fm, "partial_frac": pm}
                       for p, c, a, fl, by, (fm, pm) in zip(ps, cls_ms, att_ms, flops_p, bytes_p, mix)],
+            "list_granularities_p0.5": granularities,
             "e2e": {"value": flops_all / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": args.steps * n_p * 3,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps,
+                    "copy_only_ms_per_step": copy_ms / e2e_steps,
+                    "frac_of_copy_ceiling": copy_ms / e2e_ms,
+                    "copy_gbs_per_direction_per_gpu": [h2d / (copy_ms / e2e_steps * 1e-3) / 1e9,
+                                                       d2h / (copy_ms / e2e_steps * 1e-3) / 1e9],
+                    "host_affinity": numa,
+                    "note": "copy_only = the same pinned buffers, streams and events with the kernels left out: "
+                            "what the host links allow at this N"},
+            "gpu_launches": args.steps * n_p * 2,
             "clocks": clocks,
         }
-        if world == 1 and args.comparators:
-            line["comparators"] = gpu_comparators(q, k, v, masks, ps, flops_p)
+        if sharded is not None:
+            line["sharded"] = sharded
+        if comparators is not None:
+            line["comparators"] = comparators
+        line["attention_results"] = ta_results(B, H, S, D, ps, frac_unmasked, att_ms, comparators)
+        if args.results_json:
+            with open(args.results_json, "w") as f:
+                json.dump(line["attention_results"], f, indent=2)
         if world == 1 and not args.no_cpu_baseline:
             val, sec, desc, cores = cpu_sample(args.cpu_heads, 1, 1)
             line["cpu_baseline"] = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
@@ -401,23 +651,37 @@ def run_ours(args):
         torch.distributed.destroy_process_group()
 
 
-def gpu_comparators(q, k, v, masks, ps, flops_p):
-    """Same-box library comparators of the reference's harness (test_attn.py:64): torch SDPA without a
-    mask (the vendor's dense kernel) and with the bool mask, timed like the reference times them (CUDA
-    events, best of a few runs).  Off by default; the figures are not part of the metric."""
-    import torch
-    import torch.nn.functional as F
+def ta_results(B, H, S, D, ps, frac_unmasked, sparse_ms, comparators):
+    """The per-p records of the reference harness (test_attn.py:91-128: ``attention_results.json``) for this
+    run: ``p`` there is the fraction of blocks KEPT (1 - drop probability), ``useful_flops`` is the dense
+    FLOP count times the fraction of True mask elements (test_attn.py:105-108), and the sparse time is
+    stage 2 alone with the lists passed in (test_attn.py:65)."""
+    total_flops = 2 * 2 * B * H * S * S * D                                    # test_attn.py:84
+    ref_ms = {r["p"]: r.get("ms") for r in (comparators or {}).get("sdpa_bool_mask", []) if "ms" in r}
+    ext = (comparators or {}).get("reference_package", {})
+    flex_ms = {r["p"]: r.get("flex_ms") for r in ext.get("rows", []) if r.get("flex_ms") is not None}
+    tri_ms = {r["p"]: r.get("triton_attn_ms") for r in ext.get("rows", []) if r.get("triton_attn_ms") is not None}
+    rows = []
+    for p, fu, t in zip(ps, frac_unmasked, sparse_ms):
+        useful = total_flops * fu
+        row = {"p": 1.0 - p, "drop_p": p, "fraction_unmasked": fu, "useful_flops": useful,
+               "sparse_time_ms": t, "sparse_tflops_per_sec": useful / (t / 1000) / 1e12}
+        for name, table in (("ref", ref_ms), ("flex", flex_ms), ("reference_triton", tri_ms)):
+            if p in table:
+                row[f"{name}_time_ms"] = table[p]
+                row[f"{name}_tflops_per_sec"] = useful / (table[p] / 1000) / 1e12
+        rows.append(row)
+    return {"config": {"shape": [B, H, S, S], "BLOCK_Q": BQ, "BLOCK_K": BK, "total_flops": total_flops},
+            "results": rows}
 
-    def best_ms(fn, n=5, warm=2):
-        for _ in range(warm):
-            fn()
-        torch.cuda.synchronize()
-        ts = []
-        for _ in range(n):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(); fn(); b.record(); torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b))
-        return min(ts)
+
+def gpu_comparators(q, k, v, masks, ps, flops_p):
+    """Same-GPU comparators of the reference's harness (test_attn.py:64-68), timed like the reference times
+    them (CUDA events, best of a few runs after a warm-up): torch SDPA without a mask (the vendor's dense
+    kernel) and with the bool mask, in this process; the reference's own Triton kernels and FlexAttention
+    in a child process that imports the reference package from ``baseline/_ref`` (the same inputs are
+    rebuilt there from the seeds).  The figures are not part of the metric."""
+    import torch.nn.functional as F
 
     B, H, S, D = q.shape
     dense = 4.0 * B * H * S * S * D
@@ -432,7 +696,43 @@ def gpu_comparators(q, k, v, masks, ps, flops_p):
         except Exception as e:                      # a backend that cannot take the mask
             rows.append({"p": p, "unavailable": repr(e)[:120]})
     out["sdpa_bool_mask"] = rows
+    out["reference_package"] = reference_package_comparators(B, H, S, D, ps)
     return out
+
+
+def reference_package_comparators(B, H, S, D, ps, timeout_s=420):
+    """Runs ``baseline/reference_comparators.py`` (the reference's Triton kernels and FlexAttention on the
+    headline inputs) in a child process and returns what it printed; ``unavailable`` with the reason when
+    the reference package is not there, the child fails or runs out of time."""
+    script = os.path.join(ROOT, "baseline", "reference_comparators.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "sparseattention")):
+        return {"unavailable": "baseline/_ref/sparseattention is not present on this machine"}
+    cmd = [sys.executable, script, "--B", str(B), "--H", str(H), "--S", str(S), "--D", str(D),
+           "--ps", ",".join(str(p) for p in ps)]
+    rec = {"rows": []}
+    by_p = {}
+
+    def take(text):
+        for ln in (text or "").splitlines():
+            if ln.startswith("{"):
+                part = json.loads(ln)
+                if "row" in part:                  # rows of the same p (Triton part, Flex part) are merged
+                    by_p.setdefault(part["row"]["p"], {}).update(part["row"])
+                else:
+                    rec.update(part)
+        rec["rows"] = [by_p[p] for p in sorted(by_p)]
+
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
+        take(res.stdout)                           # the child prints one JSON object per finished part
+        if res.returncode != 0:
+            rec["unavailable"] = ("child exited with " + str(res.returncode) + ": " + res.stderr.strip()[-300:])
+    except subprocess.TimeoutExpired as e:
+        take(e.stdout.decode() if isinstance(e.stdout, bytes) else e.stdout)
+        rec["unavailable"] = f"child did not finish within {timeout_s} s (parts that finished are kept)"
+    except Exception as e:
+        rec["unavailable"] = repr(e)[:300]
+    return rec
 
 
 def _quiet_stdout():
@@ -452,8 +752,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-heads", type=int, default=4, help="heads in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--comparators", action="store_true",
-                    help="N=1: also time torch SDPA (dense, and with the bool mask) on the same inputs")
+    ap.add_argument("--no-comparators", action="store_true",
+                    help="N=1: skip torch SDPA / FlexAttention / reference-Triton timings on the same inputs")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sharded multi-GPU configuration")
+    ap.add_argument("--results-json", default="", help="also write the attention_results record to this file")
     ap.add_argument("--profile", action="store_true",
                     help="profiling run: kernels only (no end-to-end leg, no CPU baseline, no warm-up floor)")
     ap.add_argument("--workload", default="headline", choices=["headline", "document", "composed", "scaling"],

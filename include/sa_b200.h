@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define SA_ABI_VERSION 2
+#define SA_ABI_VERSION 3
 
 /* status codes */
 #define SA_OK                     0
@@ -41,7 +41,8 @@ extern "C" {
 /* values written to *dev_status by the attention kernel (0 = no device-side problem) */
 #define SA_DEV_OK             0
 #define SA_DEV_WAIT_EXPIRED   1   /* a bounded mbarrier wait ran out; the output is not valid */
-#define SA_DEV_BAD_INDEX      2   /* a kv-block id outside [0, Sk/BLOCK_K) was found in a list */
+#define SA_DEV_BAD_INDEX      2   /* a kv-block id outside [0, Sk/BLOCK_K) was found in a list, or (generic
+                                     kernel) a list length outside [0, Sk/BLOCK_K]; such entries are skipped */
 
 int sa_abi_version(void);
 const char* sa_status_str(int status);
@@ -52,8 +53,16 @@ const char* sa_status_str(int status);
  * [*Bu, *Hu] with Bu = (stride_b == 0 ? 1 : B), Hu = (stride_h == 0 ? 1 : H). */
 int sa_unique_planes(int B, int H, int64_t stride_b, int64_t stride_h, int* Bu, int* Hu);
 
-/* Bytes of scratch sa_classify_mask needs (per-cell flag bytes between its two kernels). */
+/* Bytes of scratch sa_classify_mask needs for any BLOCK_Q, BLOCK_K: the words through which the warps
+ * that stream the mask hand the tile flags of a query block to the warp that builds its lists, and a
+ * few counters.  8-byte aligned device memory. */
 size_t sa_classify_workspace_bytes(int Bu, int Hu, int Sq, int Sk);
+
+/* What the caller knows about the contents of a classifier workspace. */
+#define SA_WS_UNKNOWN  0   /* anything (fresh allocation): the call clears it on the stream first (one small memset) */
+#define SA_WS_CLEAN    1   /* zero-filled by the caller, or last used by a sa_classify_mask call that has run
+                              to completion: the kernel leaves the workspace zero-filled, so a workspace that
+                              is kept between calls needs clearing only once */
 
 /* Stage 1: block classifier.  Replaces compute_mask_kernel / _compute_mask_inner
  * (sparseattention/mask_utils.py:85-107, 47-82).
@@ -61,21 +70,22 @@ size_t sa_classify_workspace_bytes(int Bu, int Hu, int Sq, int Sk);
  * mask: bool bytes [B,H,Sq,Sk] (non-zero = attend) with element strides; stride_k
  *   must be 1 and every row start 16-byte aligned (else SA_ERR_UNSUPPORTED: make it
  *   contiguous first).  Sq % BLOCK_Q == 0 and Sk % BLOCK_K == 0 as in
- *   mask_utils.py:89-90; BLOCK_Q and BLOCK_K multiples of 32.
+ *   mask_utils.py:89-90; BLOCK_Q and BLOCK_K multiples of 32, BLOCK_Q at most 1024.
  * full_ids, part_ids: int32 [Bu,Hu,Sq/BLOCK_Q,Sk/BLOCK_K] contiguous; ascending kv-block
  *   ids of the fully-unmasked / partially-masked tiles of each query block, tail -1
  *   (mask_utils.py:72-79; the reference leaves the tail uninitialised).
  * full_lens, part_lens: int32 [Bu,Hu,Sq/BLOCK_Q] contiguous (mask_utils.py:81-82).
  * packed_bits: optional uint32 [Bu,Hu,Sk/32,Sq]; bit j of word [.,.,c,r] = mask[.,.,r,32c+j].
  *   Stage 2's tcgen05 kernel stages partial tiles from this plane instead of the byte mask.
- * workspace: sa_classify_workspace_bytes() bytes of device memory. */
+ * workspace: sa_classify_workspace_bytes() bytes of device memory; workspace_state: SA_WS_UNKNOWN or
+ *   SA_WS_CLEAN.  Calls that may overlap on the GPU need a workspace each. */
 int sa_classify_mask(const uint8_t* mask,
                      int64_t stride_b, int64_t stride_h, int64_t stride_q, int64_t stride_k,
                      int B, int H, int Sq, int Sk, int BLOCK_Q, int BLOCK_K,
                      int32_t* full_ids, int32_t* full_lens,
                      int32_t* part_ids, int32_t* part_lens,
                      uint32_t* packed_bits,
-                     void* workspace, size_t workspace_bytes,
+                     void* workspace, size_t workspace_bytes, int workspace_state,
                      void* stream);
 
 /* No counterpart in the reference.  The same classification as sa_classify_mask() for hosts that
@@ -85,8 +95,9 @@ int sa_classify_mask(const uint8_t* mask,
  * library, SA_STATIC_SCRATCH_BYTES long, resident on every GPU that loads the library; the call
  * allocates nothing.  Masks whose scratch need (sa_classify_workspace_bytes) exceeds it are refused
  * with SA_ERR_WORKSPACE.  The first call on a device looks the array's address up (set-up work: make
- * that call before starting any stream capture).  All calls share the array, so calls that may
- * overlap on the GPU must be serialised by the caller. */
+ * that call before starting any stream capture; the address stays valid for the lifetime of the
+ * device's primary context).  All calls share the array, which each call finds and leaves zero-filled,
+ * so calls that may overlap on the GPU must be serialised by the caller. */
 #define SA_STATIC_SCRATCH_BYTES (1u << 20)
 int sa_classify_mask_static(const uint8_t* mask,
                             int64_t stride_b, int64_t stride_h, int64_t stride_q, int64_t stride_k,

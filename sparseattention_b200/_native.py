@@ -17,11 +17,12 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("SPARSEATTN_B200_LIB") or os.path.join(_PKG_DIR, "libsparseattn_b200.so")
 
 # mirrors of the header's constants
-SA_ABI_VERSION = 2
+SA_ABI_VERSION = 3
 SA_OK = 0
 SA_DTYPE_F32, SA_DTYPE_F16, SA_DTYPE_BF16 = 0, 1, 2
 SA_IMPL_AUTO, SA_IMPL_SIMT, SA_IMPL_TCGEN05 = 0, 1, 2
 SA_DEV_OK, SA_DEV_WAIT_EXPIRED, SA_DEV_BAD_INDEX = 0, 1, 2
+SA_WS_UNKNOWN, SA_WS_CLEAN = 0, 1
 
 IMPLS = {"auto": SA_IMPL_AUTO, "simt": SA_IMPL_SIMT, "tcgen05": SA_IMPL_TCGEN05}
 _DTYPES = {torch.float32: SA_DTYPE_F32, torch.float16: SA_DTYPE_F16, torch.bfloat16: SA_DTYPE_BF16}
@@ -34,7 +35,7 @@ SYMBOLS = {
     "sa_status_str": (ctypes.c_char_p, [_i]),
     "sa_unique_planes": (_i, [_i, _i, _i64, _i64, _pi, _pi]),
     "sa_classify_workspace_bytes": (_sz, [_i, _i, _i, _i]),
-    "sa_classify_mask": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _p]),
+    "sa_classify_mask": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _sz, _i, _p]),
     "sa_classify_mask_static": (_i, [_p, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "sa_merge_lists": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "sa_attn_uses_tcgen05": (_i, [_i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p, _i]),
@@ -125,6 +126,25 @@ def _canonical_mask(mask: torch.Tensor) -> torch.Tensor:
     return base
 
 
+# Classifier workspaces kept between calls, one per (device, stream): the kernel needs its workspace
+# zero-filled and leaves it zero-filled, so a kept workspace is cleared once, when it is made.
+_CLASSIFY_WS = {}
+
+
+def _classify_workspace(dev: torch.device, n_bytes: int) -> torch.Tensor:
+    """A zero-filled workspace of at least ``n_bytes`` for the current stream of ``dev``.  While a CUDA
+    graph is being captured a fresh one is made inside the capture instead (memory that a graph's pool
+    owns must not be kept for use outside it)."""
+    if torch.cuda.is_current_stream_capturing():
+        return torch.zeros((n_bytes,), dtype=torch.uint8, device=dev)
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _CLASSIFY_WS.get(key)
+    if ws is None or ws.numel() < n_bytes:
+        ws = torch.zeros((max(n_bytes, 1 << 16),), dtype=torch.uint8, device=dev)
+        _CLASSIFY_WS[key] = ws
+    return ws
+
+
 @torch.library.custom_op("sparseattention::classify_mask", mutates_args=())
 def classify_mask_op(mask: torch.Tensor, block_q: int, block_k: int,
                      with_bits: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -147,14 +167,14 @@ def classify_mask_op(mask: torch.Tensor, block_q: int, block_k: int,
         bits = (torch.empty((Bu, Hu, Sk // 32, Sq), dtype=torch.int32, device=dev) if with_bits
                 else torch.empty((0,), dtype=torch.int32, device=dev))
         ws_bytes = lib.sa_classify_workspace_bytes(Bu, Hu, Sq, Sk)
-        ws = torch.empty((max(ws_bytes, 1),), dtype=torch.uint8, device=dev)
+        ws = _classify_workspace(dev, ws_bytes)
         sb = mask.stride(0) if Bu > 1 else 0
         sh = mask.stride(1) if Hu > 1 else 0
         rc = lib.sa_classify_mask(mask.data_ptr(), sb, sh, mask.stride(2), mask.stride(3),
                                   Bu, Hu, Sq, Sk, block_q, block_k,
                                   full_ids.data_ptr(), full_lens.data_ptr(), part_ids.data_ptr(), part_lens.data_ptr(),
                                   bits.data_ptr() if with_bits else None,
-                                  ws.data_ptr(), ws_bytes, _stream_ptr(dev))
+                                  ws.data_ptr(), ws.numel(), SA_WS_CLEAN, _stream_ptr(dev))
     _check(rc, "sa_classify_mask")
     return full_ids, full_lens, part_ids, part_lens, bits
 

@@ -1,8 +1,26 @@
 // extern "C" entry points declared in include/sa_b200.h: argument validation and dispatch.
 #include <cstring>
-#include <cstdlib>
+#include <mutex>
 
 #include "sa_common.cuh"
+
+namespace sa {
+
+const DeviceInfo* current_device_info() {
+  static std::once_flag once[kMaxDevices];
+  static DeviceInfo info[kMaxDevices];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::call_once(once[dev], [dev] {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
+    info[dev].ordinal = dev;
+    info[dev].sm_count = sms;
+  });
+  return info[dev].sm_count > 0 ? &info[dev] : nullptr;
+}
+
+}  // namespace sa
 
 namespace {
 
@@ -39,8 +57,11 @@ int sa_unique_planes(int B, int H, int64_t stride_b, int64_t stride_h, int* Bu, 
 
 size_t sa_classify_workspace_bytes(int Bu, int Hu, int Sq, int Sk) {
   if (!positive(Bu) || !positive(Hu) || !positive(Sq) || !positive(Sk)) return 0;
-  const size_t cells = static_cast<size_t>(Bu) * Hu * (Sq / sa::kCell) * (Sk / sa::kCell);
-  return (cells + 255) & ~static_cast<size_t>(255);
+  if (static_cast<long long>(Bu) * Hu > 0x7fffffffLL) return 0;
+  // sized for the shortest query blocks (32 rows), whatever BLOCK_Q a call then uses
+  const int chunks = (Sk + sa::kStripBytes - 1) / sa::kStripBytes;
+  const size_t bytes = sa::classify_workspace_layout(Bu * Hu, (Sq + sa::kCell - 1) / sa::kCell, chunks, nullptr, nullptr);
+  return (bytes + 255) & ~static_cast<size_t>(255);
 }
 
 int sa_classify_mask(const uint8_t* mask,
@@ -49,7 +70,7 @@ int sa_classify_mask(const uint8_t* mask,
                      int32_t* full_ids, int32_t* full_lens,
                      int32_t* part_ids, int32_t* part_lens,
                      uint32_t* packed_bits,
-                     void* workspace, size_t workspace_bytes,
+                     void* workspace, size_t workspace_bytes, int workspace_state,
                      void* stream) {
   if (mask == nullptr || full_ids == nullptr || full_lens == nullptr || part_ids == nullptr || part_lens == nullptr)
     return SA_ERR_INVALID_ARGUMENT;
@@ -57,6 +78,8 @@ int sa_classify_mask(const uint8_t* mask,
     return SA_ERR_INVALID_ARGUMENT;
   if (Sq % BLOCK_Q != 0 || Sk % BLOCK_K != 0) return SA_ERR_INVALID_ARGUMENT;        // mask_utils.py:89-90
   if (BLOCK_Q % sa::kCell != 0 || BLOCK_K % sa::kCell != 0) return SA_ERR_UNSUPPORTED;
+  if (BLOCK_Q > 32 * sa::kCell) return SA_ERR_UNSUPPORTED;       // one arrival bit per 32-row slice of a query block
+  if (workspace_state != SA_WS_UNKNOWN && workspace_state != SA_WS_CLEAN) return SA_ERR_INVALID_ARGUMENT;
   if (stride_k != 1 || stride_q < Sk || stride_q % 16 != 0 || stride_b % 16 != 0 || stride_h % 16 != 0 ||
       stride_b < 0 || stride_h < 0 || reinterpret_cast<uintptr_t>(mask) % 16 != 0)
     return SA_ERR_UNSUPPORTED;
@@ -64,16 +87,19 @@ int sa_classify_mask(const uint8_t* mask,
   int Bu = 1, Hu = 1;
   sa_unique_planes(B, H, stride_b, stride_h, &Bu, &Hu);
   const size_t need = sa_classify_workspace_bytes(Bu, Hu, Sq, Sk);
-  if (workspace == nullptr || workspace_bytes < need) return SA_ERR_WORKSPACE;
+  if (workspace == nullptr || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 8 != 0)
+    return SA_ERR_WORKSPACE;
+  if (static_cast<long long>(Bu) * Hu * (Sq / BLOCK_Q) > 0x7fffffffLL) return SA_ERR_UNSUPPORTED;
 
-  sa::ClassifyParams p;
+  sa::ClassifyParams p = {};
   p.mask = mask;
   p.stride_b = stride_b; p.stride_h = stride_h; p.stride_q = stride_q;
   p.Bu = Bu; p.Hu = Hu; p.Sq = Sq; p.Sk = Sk; p.BQ = BLOCK_Q; p.BK = BLOCK_K;
-  p.cells = static_cast<uint8_t*>(workspace);
   p.bits = packed_bits;
   p.full_ids = full_ids; p.full_lens = full_lens; p.part_ids = part_ids; p.part_lens = part_lens;
-  return sa::launch_classify(p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
+  return sa::launch_classify(p, workspace, workspace_state == SA_WS_UNKNOWN, static_cast<cudaStream_t>(stream)) ==
+                 cudaSuccess
+             ? SA_OK : SA_ERR_CUDA;
 }
 
 int sa_merge_lists(const int32_t* full_ids_in, const int32_t* full_lens_in,
@@ -175,9 +201,6 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   if (workspace != nullptr && workspace_bytes >= sa_attn_workspace_bytes() &&
       reinterpret_cast<uintptr_t>(workspace) % 4 == 0)
     p.tile_counter = static_cast<int32_t*>(workspace);
-#ifdef SA_TRACE
-  { const char* e = getenv("SA_TC_DEBUG"); p.debug = e ? atoi(e) : 0; }
-#endif
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   const bool tc_ok = sa::attn_tc_supported(p) != 0;

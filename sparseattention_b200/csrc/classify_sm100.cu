@@ -3,16 +3,28 @@
 // Replaces sparseattention/mask_utils.py:47-107 (_compute_mask_inner + its launcher).
 // The reference walks the kv blocks of one query block serially in one program and
 // re-reads an expanded mask once per head; here every distinct mask byte is read
-// exactly once with 16-byte loads:
+// exactly once with 16-byte loads, by ONE kernel:
 //
-//   cells kernel   one warp per 32-row x 512-column strip: each lane streams 32 rows of
-//                  16 bytes, reduces them to "any / all" flags of the 32x32 cells (a lane
-//                  pair per cell) and, optionally, emits the packed bit-plane stage 2 reads.
-//   lists kernel   one CTA per (mask plane, query block), launched as a programmatic
-//                  dependent of the cells kernel: folds the cell flags of each
-//                  BLOCK_Q x BLOCK_K tile, ballots the full / partial predicates and writes the
-//                  ascending id lists by a popcount prefix (order of mask_utils.py:66-79),
-//                  tails filled with -1.
+//   streaming   one warp per strip of 32 rows x 512 columns: each lane streams 32 rows of 16 bytes,
+//               reduces them to "any / all" flags of the 32x32 cells (a lane pair per cell) and,
+//               optionally, emits the packed bit-plane stage 2 reads.  The grid is SMs x resident CTAs
+//               (four of 256 threads per SM); every warp strides over the strips.
+//   flags       the 16 cells of a strip travel as one 64-bit atomic OR into a word per (plane, query
+//               block, strip column): 16 "any" bits, 16 "not all" bits and one arrival bit per cell
+//               row of the query block.  The warp whose OR completes a word counts it on the query
+//               block; the warp that counts the last word of a query block has, by then, every flag
+//               of that block in front of it.
+//   lists       that warp folds the flags of each BLOCK_Q x BLOCK_K tile, ballots the full / partial
+//               predicates and writes the ascending id lists by popcount prefixes (order of
+//               mask_utils.py:66-79), tails filled with -1, and puts the words and the counter back
+//               to zero (it fetches the words with atomic exchanges that leave zero behind).  List building thus overlaps the streaming of the rest of the mask; only the
+//               last query block's lists are built after the last byte has arrived.
+//
+// Scratch: the words and counters (sa_classify_workspace_bytes).  They must be zero when the kernel
+// starts and are zero again when it ends.
+#include <atomic>
+#include <mutex>
+
 #include "sa_common.cuh"
 
 namespace sa {
@@ -25,31 +37,151 @@ __device__ __forceinline__ uint4 ld_stream_16(const uint8_t* p) {
   return v;
 }
 
-// 4 mask bytes -> 4 bits (bit i = byte i non-zero).
-__device__ __forceinline__ uint32_t nibble_of(uint32_t w) {
-  uint32_t nz = (((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) >> 7;
-  nz &= 0x01010101u;
-  return (nz * 0x01020408u) >> 24;   // gathers bits 0,8,16,24 into bits 0..3
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(selector));
+  return r;
 }
 
-__device__ __forceinline__ uint32_t half_word_of(const uint4& v) {
-  return nibble_of(v.x) | (nibble_of(v.y) << 4) | (nibble_of(v.z) << 8) | (nibble_of(v.w) << 12);
+// 16 mask bytes, each 0 or 1 -> 16 bits in the low half of the result (bit i = byte i); the upper half
+// is not meaningful.  A multiply gathers the four low bits of a word's bytes into its top byte (into the
+// low nibble with one constant, the high nibble with the other), so two words share a byte.
+__device__ __forceinline__ uint32_t bits_of_01(const uint4& v) {
+  const uint32_t a = (v.x * 0x01020408u) | (v.y * 0x10204080u);
+  const uint32_t b = (v.z * 0x01020408u) | (v.w * 0x10204080u);
+  return prmt(a, b, 0x0073u);            // byte 0 <- top byte of a, byte 1 <- top byte of b
+}
+
+// Any non-zero byte -> 1 (torch bool storage is 0 / 1 already; a mask viewed from other bytes may not be).
+__device__ __forceinline__ uint32_t to_01(uint32_t w) {
+  return ((((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) >> 7) & 0x01010101u;
 }
 
 constexpr int kCellsThreads = 256;
+constexpr int kWarpsPerCta = kCellsThreads / 32;
+constexpr int kCellsPerStrip = kStripBytes / kCell;       // 16
 
-__global__ void __launch_bounds__(kCellsThreads)
-classify_cells_kernel(const ClassifyParams p, const int chunks_per_row, const long long n_strips) {
-  // lets the lists kernel be scheduled early; it waits for this grid to complete before reading
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+// The lists of one (plane, query block) from its flag words, by one warp.  words[c]: bits 0-15 "any
+// True" and bits 16-31 "not all True" of the 16 cell columns of strip column c, ORed over the cell
+// rows of the query block.  The words are fetched with an atomic exchange that leaves zero behind
+// (every atomic on a word is performed where the word lives, so the exchange returns every
+// contribution that was acknowledged before it); 32 tiles per pass, one per lane.
+__device__ __forceinline__ void build_lists_warp(const ClassifyParams& p, unsigned long long* words,
+                                                 int chunks_per_row, int row) {
   const int lane = threadIdx.x & 31;
-  const long long warp0 = (static_cast<long long>(blockIdx.x) * kCellsThreads + threadIdx.x) >> 5;
-  const long long n_warps = (static_cast<long long>(gridDim.x) * kCellsThreads) >> 5;
+  const int nk = p.Sk / p.BK;
+  const int rk = p.BK / kCell;
+  int32_t* f_out = p.full_ids + static_cast<int64_t>(row) * nk;
+  int32_t* p_out = p.part_ids + static_cast<int64_t>(row) * nk;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  int nf = 0, np = 0;
+  auto emit = [&](int j, bool live, bool any, bool all) {
+    const bool is_full = live && all;                                  // count == BQ*BK  (mask_utils.py:72)
+    const bool is_part = live && !all && any;                          // 0 < count       (mask_utils.py:76)
+    const uint32_t bf = __ballot_sync(0xffffffffu, is_full);
+    const uint32_t bp = __ballot_sync(0xffffffffu, is_part);
+    if (is_full) f_out[nf + __popc(bf & lt_mask)] = j;
+    if (is_part) p_out[np + __popc(bp & lt_mask)] = j;
+    nf += __popc(bf);
+    np += __popc(bp);
+  };
+  if (chunks_per_row <= 32 || (32 * kCellsPerStrip) % rk == 0) {
+    // 32 strip columns (512 cell columns) at a time, lane l holding word w0 + l: no tile straddles two
+    // such groups
+    for (int w0 = 0; w0 < chunks_per_row; w0 += 32) {
+      const uint32_t mine = (w0 + lane < chunks_per_row)
+          ? static_cast<uint32_t>(atomicExch(words + w0 + lane, 0ull)) : 0u;
+      const int cell_end = min((w0 + 32) * kCellsPerStrip, p.Sk / kCell);
+      for (int j0 = w0 * kCellsPerStrip / rk; j0 * rk < cell_end; j0 += 32) {
+        const int j = j0 + lane;
+        bool any = false, all = true;
+        for (int x = 0; x < rk; ++x) {
+          const int cc = j * rk + x;                                   // cell column
+          const uint32_t w = __shfl_sync(0xffffffffu, mine, ((cc >> 4) - w0) & 31);
+          any = any || ((w >> (cc & 15)) & 1u);
+          all = all && !((w >> (16 + (cc & 15))) & 1u);
+        }
+        emit(j, j * rk < cell_end && j < nk, any, all);
+      }
+    }
+  } else {
+    // long rows with a BLOCK_K whose tiles can straddle a group of 32 words: every lane reads the words
+    // of its tile itself (an atomic OR of nothing returns the word), and the words are cleared afterwards
+    for (int j0 = 0; j0 < nk; j0 += 32) {
+      const int j = j0 + lane;
+      bool any = false, all = true;
+      if (j < nk) {
+        for (int x = 0; x < rk; ++x) {
+          const int cc = j * rk + x;
+          const uint32_t w = static_cast<uint32_t>(atomicOr(words + (cc >> 4), 0ull));
+          any = any || ((w >> (cc & 15)) & 1u);
+          all = all && !((w >> (16 + (cc & 15))) & 1u);
+        }
+      }
+      emit(j, j < nk, any, all);
+    }
+    __syncwarp();
+    for (int c = lane; c < chunks_per_row; c += 32) atomicExch(words + c, 0ull);
+  }
+  for (int t = nf + lane; t < nk; t += 32) f_out[t] = -1;
+  for (int t = np + lane; t < nk; t += 32) p_out[t] = -1;
+  if (lane == 0) {
+    p.full_lens[row] = nf;                                             // mask_utils.py:81
+    p.part_lens[row] = np;                                             // mask_utils.py:82
+  }
+}
+
+// 32 rows x 16 bytes of one lane -> the lane's AND / OR accumulators over the rows (16 bits each) and,
+// exchanged with the neighbour lane, the 32-bit row words of the lane pair's cell: even lanes keep rows
+// 0..15 of the cell, odd lanes rows 16..31.  kNormalise: bytes other than 0 / 1 may occur.
+template <bool kNormalise>
+__device__ __forceinline__ void reduce_strip(const uint8_t* src, int64_t stride_q, bool active, int odd,
+                                             uint32_t& and_acc, uint32_t& or_acc, uint32_t& raw_or,
+                                             uint32_t (&keep)[16]) {
+  const uint32_t selector = odd ? 0x1054u : 0x5410u;       // (mine, other) -> columns in ascending order
+  and_acc = 0xffffu;
+  or_acc = 0u;
+  raw_or = 0u;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint4 v[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      v[r] = active ? ld_stream_16(src + static_cast<int64_t>(g * 8 + r) * stride_q) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const int row = g * 8 + r;
+      if (kNormalise) {
+        v[r].x = to_01(v[r].x); v[r].y = to_01(v[r].y); v[r].z = to_01(v[r].z); v[r].w = to_01(v[r].w);
+      } else {
+        raw_or |= v[r].x | v[r].y;
+        raw_or |= v[r].z | v[r].w;
+      }
+      const uint32_t hb = bits_of_01(v[r]);
+      and_acc &= hb;
+      or_acc |= hb;
+      const uint32_t other = __shfl_xor_sync(0xffffffffu, hb, 1);
+      const uint32_t word = prmt(hb, other, selector);
+      if ((row >> 4) == 0) { if (!odd) keep[row & 15] = word; }
+      else                 { if (odd)  keep[row & 15] = word; }
+    }
+  }
+  and_acc &= 0xffffu;
+  or_acc &= 0xffffu;
+}
+
+__global__ void __launch_bounds__(kCellsThreads, 4)
+classify_kernel(const ClassifyParams p, const int chunks_per_row, const long long n_strips) {
+  const int lane = threadIdx.x & 31;
   const int row_cells = p.Sq / kCell;
   const int col_cells = p.Sk / kCell;
+  const int rq = p.BQ / kCell, nq = p.Sq / p.BQ;
   const int odd = lane & 1;
+  const unsigned long long done_all = rq >= 32 ? 0xffffffffull : ((1ull << rq) - 1ull);
+  const long long n_warps = (static_cast<long long>(gridDim.x) * kCellsThreads) >> 5;
 
-  for (long long strip = warp0; strip < n_strips; strip += n_warps) {
+  for (long long strip = (static_cast<long long>(blockIdx.x) * kCellsThreads + threadIdx.x) >> 5; strip < n_strips;
+       strip += n_warps) {
     const int chunk = static_cast<int>(strip % chunks_per_row);
     const long long t = strip / chunks_per_row;
     const int rc = static_cast<int>(t % row_cells);
@@ -57,47 +189,55 @@ classify_cells_kernel(const ClassifyParams p, const int chunks_per_row, const lo
     const int b = plane / p.Hu, h = plane % p.Hu;
     const int col = chunk * kStripBytes + lane * 16;
     const bool active = col < p.Sk;
-    const uint8_t* base = p.mask + b * p.stride_b + h * p.stride_h +
-                          static_cast<int64_t>(rc) * kCell * p.stride_q + col;
+    const uint8_t* src = p.mask + b * p.stride_b + h * p.stride_h +
+                         static_cast<int64_t>(rc) * kCell * p.stride_q + col;
 
-    uint32_t and_acc = 0xffffu, or_acc = 0u;
+    uint32_t and_acc, or_acc, raw_or;
     uint32_t keep[16];
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      uint4 v[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        v[r] = active ? ld_stream_16(base + static_cast<int64_t>(g * 8 + r) * p.stride_q)
-                      : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const int row = g * 8 + r;
-        const uint32_t hb = half_word_of(v[r]);
-        and_acc &= hb;
-        or_acc |= hb;
-        const uint32_t other = __shfl_xor_sync(0xffffffffu, hb, 1);
-        const uint32_t word = odd ? (other | (hb << 16)) : (hb | (other << 16));
-        // even lanes keep rows 0..15 of the cell, odd lanes rows 16..31
-        if ((row >> 4) == 0) { if (!odd) keep[row & 15] = word; }
-        else                 { if (odd)  keep[row & 15] = word; }
-      }
-    }
+    reduce_strip<false>(src, p.stride_q, active, odd, and_acc, or_acc, raw_or, keep);
+    if (__any_sync(0xffffffffu, (raw_or & 0xfefefefeu) != 0u))          // bytes other than 0 / 1: once more, normalised
+      reduce_strip<true>(src, p.stride_q, active, odd, and_acc, or_acc, raw_or, keep);
     const uint32_t and_all = and_acc & __shfl_xor_sync(0xffffffffu, and_acc, 1);
     const uint32_t or_any = or_acc | __shfl_xor_sync(0xffffffffu, or_acc, 1);
-    if (active) {
-      const int kb = chunk * (kStripBytes / kCell) + (lane >> 1);
-      if (!odd) {
-        const uint8_t flag = static_cast<uint8_t>((or_any != 0u ? 1u : 0u) | (and_all == 0xffffu ? 2u : 0u));
-        p.cells[(static_cast<int64_t>(plane) * row_cells + rc) * col_cells + kb] = flag;
+    // cell c of the strip is owned by lanes 2c and 2c+1: bring its flags to lane c and ballot
+    const int src_lane = (lane & 15) * 2;
+    const bool any_c = __shfl_sync(0xffffffffu, or_any != 0u ? 1 : 0, src_lane) != 0;
+    const bool all_c = __shfl_sync(0xffffffffu, and_all == 0xffffu ? 1 : 0, src_lane) != 0;
+    const uint32_t any16 = __ballot_sync(0xffffffffu, any_c) & 0xffffu;
+    const uint32_t notall16 = __ballot_sync(0xffffffffu, !all_c) & 0xffffu;
+
+    // One 64-bit atomic carries the strip's flags and its arrival.  Everything the list builder needs
+    // travels inside atomics, each issued after the previous one's value has come back: a strip's OR,
+    // then (by the warp whose OR completed the word) the count on the query block, then (by the warp
+    // that counted the last word) the exchanges that fetch the words.  All of them are performed at the
+    // one place where their address lives, so an exchange returns every OR that was acknowledged before
+    // the count that led to it; no other memory is handed between warps, and no fence is needed.
+    const int qblk = rc / rq;
+    const int64_t qrow = static_cast<int64_t>(plane) * nq + qblk;
+    unsigned long long* words = p.words + qrow * chunks_per_row;
+    int build = 0;
+    if (lane == 0) {
+      const unsigned long long mine = static_cast<unsigned long long>(any16) |
+                                      (static_cast<unsigned long long>(notall16) << 16) |
+                                      (1ull << (32 + (rc % rq)));
+      const unsigned long long old = atomicOr(words + chunk, mine);
+      if ((((old | mine) >> 32) & 0xffffffffull) == done_all) {
+        const unsigned int seen = atomicAdd(p.row_counters + qrow, 1u);
+        build = seen == static_cast<unsigned int>(chunks_per_row) - 1u;
       }
-      if (p.bits != nullptr) {
-        uint4* dst = reinterpret_cast<uint4*>(
-            p.bits + (static_cast<int64_t>(plane) * col_cells + kb) * p.Sq + rc * kCell + odd * 16);
+    }
+    build = __shfl_sync(0xffffffffu, build, 0);
+    if (build) {
+      build_lists_warp(p, words, chunks_per_row, static_cast<int>(qrow));   // leaves the words zero
+      if (lane == 0) atomicExch(p.row_counters + qrow, 0u);
+    }
+    if (active && p.bits != nullptr) {
+      const int kb = chunk * kCellsPerStrip + (lane >> 1);
+      uint4* dst = reinterpret_cast<uint4*>(
+          p.bits + (static_cast<int64_t>(plane) * col_cells + kb) * p.Sq + rc * kCell + odd * 16);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          dst[i] = make_uint4(keep[4 * i], keep[4 * i + 1], keep[4 * i + 2], keep[4 * i + 3]);
-      }
+      for (int i = 0; i < 4; ++i)
+        dst[i] = make_uint4(keep[4 * i], keep[4 * i + 1], keep[4 * i + 2], keep[4 * i + 3]);
     }
   }
 }
@@ -156,20 +296,6 @@ __device__ __forceinline__ void build_lists(const ClassifyParams& p, const uint8
     p.full_lens[row] = nf;                                       // mask_utils.py:81
     p.part_lens[row] = np;                                       // mask_utils.py:82
   }
-}
-
-// One CTA per (mask plane, query block).
-__global__ void __launch_bounds__(kListsThreads)
-compact_lists_kernel(const ClassifyParams p, const int n_rows) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");     // the cell flags of the streaming kernel are complete
-  __shared__ int s_full[kListsThreads / 32], s_part[kListsThreads / 32];
-  const int row = blockIdx.x;                                       // (plane, query block)
-  if (row >= n_rows) return;
-  const int nq = p.Sq / p.BQ, rq = p.BQ / kCell;
-  const int row_cells = p.Sq / kCell, col_cells = p.Sk / kCell;
-  const int plane = row / nq, i = row % nq;
-  const uint8_t* cells = p.cells + (static_cast<int64_t>(plane) * row_cells + static_cast<int64_t>(i) * rq) * col_cells;
-  build_lists(p, cells, col_cells, row, s_full, s_part);
 }
 
 // Lists of short query blocks -> lists of the tall query blocks that contain `ratio` of them each.
@@ -233,43 +359,44 @@ merge_lists_kernel(const ClassifyParams p_out, const int32_t* __restrict__ full_
 
 }  // namespace
 
-cudaError_t launch_classify(const ClassifyParams& p, cudaStream_t stream) {
+size_t classify_workspace_layout(int planes, int nq, int chunks, size_t* off_rows, size_t* off_words) {
+  const size_t rows = static_cast<size_t>(planes) * nq;
+  const size_t o_rows = 0;
+  const size_t o_words = (o_rows + 4 * rows + 7) & ~static_cast<size_t>(7);
+  if (off_rows != nullptr) *off_rows = o_rows;
+  if (off_words != nullptr) *off_words = o_words;
+  return o_words + 8 * rows * static_cast<size_t>(chunks);
+}
+
+cudaError_t launch_classify(ClassifyParams p, void* workspace, bool clear_first, cudaStream_t stream) {
   const int planes = p.Bu * p.Hu;
   const int chunks = (p.Sk + kStripBytes - 1) / kStripBytes;
+  const int nq = p.Sq / p.BQ;
   const long long n_strips = static_cast<long long>(planes) * (p.Sq / kCell) * chunks;
-  static int sm_count = 0, cells_occ = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
+  const DeviceInfo* info = current_device_info();
+  if (info == nullptr) return cudaErrorInvalidDevice;
+  static std::once_flag once[kMaxDevices];
+  static int occupancy[kMaxDevices];
+  std::call_once(once[info->ordinal], [&] {
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, classify_kernel, kCellsThreads, 0) != cudaSuccess) occ = 0;
+    occupancy[info->ordinal] = occ > 0 ? occ : 1;
+  });
+  size_t off_rows = 0, off_words = 0;
+  const size_t bytes = classify_workspace_layout(planes, nq, chunks, &off_rows, &off_words);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.row_counters = reinterpret_cast<unsigned int*>(ws + off_rows);
+  p.words = reinterpret_cast<unsigned long long*>(ws + off_words);
+  if (clear_first) {
+    cudaError_t e = cudaMemsetAsync(ws, 0, bytes, stream);
     if (e != cudaSuccess) return e;
-    int sms = 0, occ = 0;
-    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, classify_cells_kernel, kCellsThreads, 0);
-    if (e != cudaSuccess) return e;
-    cells_occ = occ > 0 ? occ : 1;
-    sm_count = sms;
   }
-  const long long warps_per_cta = kCellsThreads / 32;
-  long long ctas = (n_strips + warps_per_cta - 1) / warps_per_cta;
-  const long long resident = static_cast<long long>(sm_count) * cells_occ;
+  long long ctas = (n_strips + kWarpsPerCta - 1) / kWarpsPerCta;
+  const long long resident = static_cast<long long>(info->sm_count) * occupancy[info->ordinal];
   if (ctas > resident) ctas = resident;      // persistent: each warp strides over the strips
   if (ctas < 1) ctas = 1;
-  classify_cells_kernel<<<static_cast<unsigned>(ctas), kCellsThreads, 0, stream>>>(p, chunks, n_strips);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  const int n_rows = planes * (p.Sq / p.BQ);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(n_rows));
-  cfg.blockDim = dim3(kListsThreads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, compact_lists_kernel, p, n_rows);
+  classify_kernel<<<static_cast<unsigned>(ctas), kCellsThreads, 0, stream>>>(p, chunks, n_strips);
+  return cudaGetLastError();
 }
 
 // p_out carries only the output pointers; its block sizes are set here so that build_lists sees one
@@ -292,25 +419,27 @@ cudaError_t launch_merge_lists(const int32_t* full_ids_in, const int32_t* full_l
 // ---------------------------------------------------------------------------------------------
 // Allocation-free variant of the classifier entry point.
 //
-// sa_classify_mask() needs a caller-provided workspace for the cell flags that travel between its
-// two kernels.  Some hosts have no way to provide one: a serving process whose device memory was
-// carved up once at start-up and is fully committed (KV caches, weights), a plugin that runs inside
-// another runtime's callback where calling the allocator is not permitted, a hard-latency loop in
-// which an allocation (and the implicit synchronisation a cudaMalloc / cudaFree can bring) is not
-// affordable.  For them the flags live in the fixed device array below: SA_STATIC_SCRATCH_BYTES
-// bytes that every GPU which loads this library holds until the process exits.
+// sa_classify_mask() needs a caller-provided workspace for the flag words and counters through which
+// the warps of its kernel hand the tile flags to the warp that builds a query block's lists.  Some
+// hosts have no way to provide one: a serving process whose device memory was carved up once at
+// start-up and is fully committed (KV caches, weights), a plugin that runs inside another runtime's
+// callback where calling the allocator is not permitted, a hard-latency loop in which an allocation
+// (and the implicit synchronisation a cudaMalloc / cudaFree can bring) is not affordable.  For them
+// the scratch lives in the fixed device array below: SA_STATIC_SCRATCH_BYTES bytes that every GPU
+// which loads this library holds until the process exits.
 //
 // The array's name is only a host-side handle; the device address is looked up once per device
 // with cudaGetSymbolAddress (with that device current) on the first call made on it.  That first
-// call therefore does set-up work and should be made before any stream capture is started.
-// Every call uses the same array: it keeps the flags of the previous call (every flag a call reads
-// is written by that call first, so nothing needs clearing), and two calls whose kernels overlap on
-// the GPU - different streams, or different host threads - race on it.  Serialise them.
+// call therefore does set-up work and should be made before any stream capture is started.  The
+// cached address is valid for the lifetime of the device's primary context.
+// Every call uses the same array.  The kernel needs it zero-filled and leaves it zero-filled (the
+// array starts out as zeros, and each word is put back to zero by the warp that consumed it), so
+// nothing is cleared between calls; two calls whose kernels overlap on the GPU - different streams,
+// or different host threads - race on it.  Serialise them.
 static __device__ __align__(256) uint8_t g_static_scratch[SA_STATIC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
-uint8_t* g_static_scratch_addr[kMaxDevices] = {};
+std::atomic<uint8_t*> g_static_scratch_addr[sa::kMaxDevices];
 }  // namespace
 
 extern "C" int sa_classify_mask_static(const uint8_t* mask,
@@ -326,13 +455,15 @@ extern "C" int sa_classify_mask_static(const uint8_t* mask,
   if (need == 0) return SA_ERR_INVALID_ARGUMENT;
   if (need > SA_STATIC_SCRATCH_BYTES) return SA_ERR_WORKSPACE;    // mask too large for the fixed array
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SA_ERR_NO_DEVICE;
-  if (g_static_scratch_addr[dev] == nullptr) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= sa::kMaxDevices) return SA_ERR_NO_DEVICE;
+  uint8_t* scratch = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     void* addr = nullptr;
     if (cudaGetSymbolAddress(&addr, g_static_scratch) != cudaSuccess || addr == nullptr) return SA_ERR_CUDA;
-    g_static_scratch_addr[dev] = static_cast<uint8_t*>(addr);
+    scratch = static_cast<uint8_t*>(addr);
+    g_static_scratch_addr[dev].store(scratch, std::memory_order_release);   // every thread finds the same value
   }
   return sa_classify_mask(mask, stride_b, stride_h, stride_q, stride_k, B, H, Sq, Sk, BLOCK_Q, BLOCK_K,
                           full_ids, full_lens, part_ids, part_lens, packed_bits,
-                          g_static_scratch_addr[dev], SA_STATIC_SCRATCH_BYTES, stream);
+                          scratch, SA_STATIC_SCRATCH_BYTES, SA_WS_CLEAN, stream);
 }

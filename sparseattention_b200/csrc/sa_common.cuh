@@ -10,6 +10,14 @@ namespace sa {
 
 constexpr int kCell = 32;            // side of the cells the classifier reduces the mask to
 constexpr int kStripBytes = 512;     // mask bytes one warp reads per row (32 lanes x 16 B)
+constexpr int kMaxDevices = 64;      // device ordinals the per-device caches cover
+
+// Facts about the current device, looked up once per device ordinal (thread-safe); nullptr on failure.
+struct DeviceInfo {
+  int ordinal;
+  int sm_count;
+};
+const DeviceInfo* current_device_info();
 
 // ---------------------------------------------------------------- stage 1
 struct ClassifyParams {
@@ -17,7 +25,11 @@ struct ClassifyParams {
   int64_t stride_b, stride_h, stride_q;   // elements (= bytes); stride_k == 1
   int Bu, Hu, Sq, Sk;
   int BQ, BK;
-  uint8_t* cells;        // [Bu*Hu, Sq/32, Sk/32] flag bytes: bit0 = any True, bit1 = all True
+  // scratch, zero before and after a launch: per (plane, query block, strip column) a 64-bit word
+  // (16 any bits, 16 not-all bits, one arrival bit per cell row) and a completed-word count per (plane,
+  // query block)
+  unsigned long long* words;
+  unsigned int* row_counters;
   uint32_t* bits;        // optional [Bu*Hu, Sk/32, Sq]
   int32_t* full_ids;     // [Bu*Hu, nq, nk]
   int32_t* full_lens;    // [Bu*Hu, nq]
@@ -25,7 +37,10 @@ struct ClassifyParams {
   int32_t* part_lens;
 };
 
-cudaError_t launch_classify(const ClassifyParams& p, cudaStream_t stream);
+// Bytes of scratch for planes x nq query blocks x chunks strip columns, and where its parts start.
+size_t classify_workspace_layout(int planes, int nq, int chunks, size_t* off_rows, size_t* off_words);
+// Points p's scratch members into `workspace` (cleared on the stream first when asked) and launches.
+cudaError_t launch_classify(ClassifyParams p, void* workspace, bool clear_first, cudaStream_t stream);
 // Lists of query blocks `ratio` times shorter -> lists of the tall blocks (p_out: output pointers only).
 cudaError_t launch_merge_lists(const int32_t* full_ids_in, const int32_t* full_lens_in, const int32_t* part_ids_in,
                                const int32_t* part_lens_in, int planes, int nq_out, int nk, int ratio,

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import os
+from collections import OrderedDict
 
 import torch
 
@@ -9,6 +10,43 @@ from . import _native
 from .mask_utils import MaskMetadata, compute_mask_kernel
 
 _EMPTY_BITS = {}
+
+# Opt-in reuse of stage 1 across calls (``sparse_attention(..., cache=True)``): the lists and the packed
+# plane of a mask are kept under the identity of its memory -- address, in-place modification counter
+# (shared by all views of the storage), shape, strides, block sizes -- so that every layer of a model
+# that attends under the same mask classifies it once (the amortisation the reference's README assumes
+# when it quotes stage 2 alone).  An entry holds a reference to the mask tensor: its memory cannot be
+# freed and handed to another tensor while the entry lives, so an address can never name a different
+# mask.  At most MASK_CACHE_ENTRIES entries, least recently used first out.
+MASK_CACHE_ENTRIES = 8
+_MASK_CACHE: "OrderedDict[tuple, tuple]" = OrderedDict()
+
+
+def clear_mask_cache() -> None:
+    """Drops every cached ``MaskMetadata`` (and the references to the masks they were made from)."""
+    _MASK_CACHE.clear()
+
+
+def _cache_key(mask: torch.Tensor, block_q: int, block_k: int) -> tuple:
+    return (mask.device.type, mask.device.index, mask.data_ptr(), mask._version, tuple(mask.shape),
+            tuple(mask.stride()), int(block_q), int(block_k))
+
+
+def cached_mask_metadata(mask: torch.Tensor, block_q: int, block_k: int) -> MaskMetadata:
+    """``compute_mask_kernel(mask, block_q, block_k)``, computed once per (mask memory, version, layout,
+    block sizes).  Writing into the mask in place (``mask[...] = ...``, ``mask.logical_and_(...)``)
+    changes its version and therefore misses; writes that bypass autograd's version counter (raw pointer
+    writes from another library) do not -- call :func:`clear_mask_cache` after those."""
+    key = _cache_key(mask, block_q, block_k)
+    hit = _MASK_CACHE.get(key)
+    if hit is not None:
+        _MASK_CACHE.move_to_end(key)
+        return hit[0]
+    md = compute_mask_kernel(mask, block_q, block_k)
+    _MASK_CACHE[key] = (md, mask)
+    while len(_MASK_CACHE) > MASK_CACHE_ENTRIES:
+        _MASK_CACHE.popitem(last=False)
+    return md
 
 
 def _no_bits(device) -> torch.Tensor:
@@ -51,7 +89,7 @@ def _merged_to_128(md: MaskMetadata, mask: torch.Tensor, block_q: int, block_k: 
 
 def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, BLOCK_Q, BLOCK_K,
                      mask_metadata: MaskMetadata = None, *, impl: str = "auto", check_status: bool = None,
-                     return_lse: bool = False):
+                     return_lse: bool = False, cache: bool = False):
     """Block-sparse attention forward: ``softmax(q k^T / sqrt(D) + where(mask, 0, -inf)) v``
     computed only over the kv blocks listed in ``mask_metadata`` (built from the mask when
     not given), exactly the call of sparse_attn_kernel.py:149.
@@ -66,6 +104,10 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     ``return_lse=True`` returns ``(out, lse)`` with ``lse`` float32 ``[B,H,Sq]``: the natural-log sum of
     exp of each row's scaled scores over its attended keys (-inf for a row with none) -- what a backward
     pass or a merge of partial attentions needs; the reference does not produce it.
+
+    ``cache=True`` (with no ``mask_metadata``) keeps the lists and the packed plane of this mask and
+    reuses them on every later call that passes the same mask memory, unmodified, with the same block
+    sizes (see :func:`cached_mask_metadata`): stage 1 then runs once per mask, not once per layer.
 
     ``check_status`` (default: the SPARSEATTN_B200_CHECK environment variable) makes the call
     read the kernel's device status word back, which synchronises; by default the call is
@@ -93,7 +135,7 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
         if merged is not None:
             md, BLOCK_Q = merged, 128
     if md is None:                              # lines 157-158
-        md = compute_mask_kernel(mask, BLOCK_Q, BLOCK_K)
+        md = cached_mask_metadata(mask, BLOCK_Q, BLOCK_K) if cache else compute_mask_kernel(mask, BLOCK_Q, BLOCK_K)
     bits = getattr(md, "packed_bits", None)
     if bits is None and impl_id != _native.SA_IMPL_SIMT and \
             _native.uses_tcgen05(q, k, v, int(BLOCK_Q), int(BLOCK_K), True):

@@ -362,3 +362,46 @@ def test_shared_key_value_heads(native_lib, impl):
     out = sa.sparse_attention(q.to(DEV), kd, vd, mask.to(DEV), 128, 32, impl=impl, check_status=True)
     torch.cuda.synchronize()
     assert_close_attn(out, ref, torch.bfloat16, f"shared kv heads {impl}")
+
+
+def test_mask_metadata_cache(native_lib, monkeypatch):
+    """``cache=True``: a second call on the same, unmodified mask runs no classifier and returns the same
+    bits; an in-place edit of the mask (or other block sizes, or another mask) classifies again."""
+    B, H, S, D = 2, 4, 1024, 128
+    q, k, v = (t.to(DEV) for t in workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=71))
+    mask = workloads.random_block_mask(B, S, 0.5, 0.2, seed=72).to(DEV)
+    sa.clear_mask_cache()
+    calls = []
+    real = native_lib.sa_classify_mask
+    monkeypatch.setattr(native_lib, "sa_classify_mask", lambda *a: (calls.append(1), real(*a))[1])
+
+    plain = sa.sparse_attention(q, k, v, mask, 128, 32, check_status=True)
+    assert len(calls) == 1
+    first = sa.sparse_attention(q, k, v, mask, 128, 32, cache=True, check_status=True)
+    assert len(calls) == 2
+    for _ in range(3):                                        # "layers" sharing the mask
+        again = sa.sparse_attention(q, k, v, mask.expand(B, H, S, S), 128, 32, cache=True, check_status=True)
+        assert torch.equal(again, first)
+    assert len(calls) == 2 and torch.equal(first, plain)
+    sa.sparse_attention(q, k, v, mask, 128, 64, cache=True)   # other block sizes: another entry
+    assert len(calls) == 3
+    mask[0, 0, :128, :] = False                               # in-place edit: the version moves
+    edited = sa.sparse_attention(q, k, v, mask, 128, 32, cache=True, check_status=True)
+    assert len(calls) == 4
+    assert_close_attn(edited, sdpa_cpu(q, k, v, mask), torch.bfloat16, "after the edit")
+    assert bool((edited[0, :, :128] == 0).all())
+    # the kernel list of a cached call holds no classifier kernel (when the profiler can see kernels here)
+    try:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            sa.sparse_attention(q, k, v, mask, 128, 32, cache=True)
+            torch.cuda.synchronize()
+        names = [e.key for e in prof.key_averages()]
+    except Exception:
+        names = []
+    if any("attn_fwd" in n for n in names):
+        assert not any("classify" in n for n in names), names
+    sa.clear_mask_cache()
+    sa.sparse_attention(q, k, v, mask, 128, 32, cache=True)
+    assert len(calls) == 5
+    sa.clear_mask_cache()

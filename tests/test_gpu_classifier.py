@@ -91,6 +91,20 @@ def test_edge_masks(native_lib):
         sa.compute_mask_kernel(torch.zeros((1, 1, 64, 64), dtype=torch.bool, device=DEV), 16, 32)
 
 
+def test_long_rows_with_tiles_that_straddle_word_groups(native_lib):
+    """Sk = 33792 (66 strips of 512 columns: more than one group of 32 flag words) with BLOCK_K = 96, whose
+    tiles do not line up with the groups, and with BLOCK_K = 32 and 1024, which do."""
+    g = torch.Generator().manual_seed(12)
+    Sq, Sk = 64, 33792
+    blocks = torch.rand((1, 1, Sq // 32, Sk // 32), generator=g)
+    m = (blocks < 0.6).repeat_interleave(32, 2).repeat_interleave(32, 3)
+    noisy = torch.rand((1, 1, Sq, Sk), generator=g) < 0.5
+    part = (blocks < 0.15).repeat_interleave(32, 2).repeat_interleave(32, 3)
+    m = (m & (~part | noisy)).to(DEV)
+    for bq, bk in [(32, 96), (64, 96), (32, 32), (64, 1024), (32, 16896)]:
+        assert_lists_equal(sa.compute_mask_kernel(m, bq, bk), oracle_lists(m, bq, bk), f"({bq},{bk})")
+
+
 def test_nonzero_bytes_count_as_true(native_lib):
     raw = torch.zeros((1, 1, 64, 64), dtype=torch.uint8, device=DEV)
     raw[0, 0, :32, :32] = 255
@@ -98,6 +112,16 @@ def test_nonzero_bytes_count_as_true(native_lib):
     raw[0, 0, 40, 40] = 0
     md = sa.compute_mask_kernel(raw.view(torch.bool), 32, 32)
     assert md.unmasked_lens.flatten().tolist() == [1, 0] and md.masked_lens.flatten().tolist() == [0, 1]
+    # arbitrary byte values over a whole plane: the lists and the packed plane are those of (byte != 0)
+    g = torch.Generator().manual_seed(3)
+    raw = torch.randint(0, 256, (2, 1, 256, 1024), generator=g, dtype=torch.uint8)
+    raw[torch.rand((2, 1, 256, 1024), generator=g) < 0.7] = 0
+    raw[:, :, :64, :128] = 128
+    raw[:, :, 64:128, 512:] = 0
+    want = raw != 0
+    md = sa.compute_mask_kernel(raw.to(DEV).view(torch.bool), 64, 32)
+    assert_lists_equal(md, oracle_lists(want, 64, 32), "raw bytes")
+    assert np.array_equal(md.packed_bits.cpu().numpy().view(np.uint32), oc.pack_bits(want.numpy()))
 
 
 @pytest.mark.parametrize("name", ["document", "composed"])
@@ -149,19 +173,29 @@ def test_c_abi_direct_call(native_lib):
     f_lens = torch.zeros((1, 1, nq), dtype=torch.int32, device=DEV)
     p_lens = torch.zeros((1, 1, nq), dtype=torch.int32, device=DEV)
     ws_bytes = native_lib.sa_classify_workspace_bytes(1, 1, 256, 256)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=DEV)
-    rc = native_lib.sa_classify_mask(m.data_ptr(), 0, 0, 256, 1, 1, 1, 256, 256, 128, 32,
-                                     f_ids.data_ptr(), f_lens.data_ptr(), p_ids.data_ptr(), p_lens.data_ptr(),
-                                     None, ws.data_ptr(), ws_bytes, torch.cuda.current_stream().cuda_stream)
-    assert rc == 0
-    torch.cuda.synchronize()
     ref = oracle_lists(m, 128, 32)
-    assert np.array_equal(f_ids.cpu().numpy(), ref.unmasked_kv_ids)
-    assert np.array_equal(p_ids.cpu().numpy(), ref.masked_kv_ids)
-    assert np.array_equal(f_lens.cpu().numpy(), ref.unmasked_lens)
-    assert np.array_equal(p_lens.cpu().numpy(), ref.masked_lens)
+    # a workspace of unknown contents (the call clears it), then a zero-filled one declared clean, used twice:
+    # the kernel hands a workspace back zero-filled
+    dirty = torch.full((ws_bytes,), 0xAB, dtype=torch.uint8, device=DEV)
+    clean = torch.zeros(ws_bytes, dtype=torch.uint8, device=DEV)
+    for ws, state in ((dirty, _native.SA_WS_UNKNOWN), (clean, _native.SA_WS_CLEAN), (clean, _native.SA_WS_CLEAN)):
+        for t in (f_ids, p_ids, f_lens, p_lens):
+            t.fill_(7)
+        rc = native_lib.sa_classify_mask(m.data_ptr(), 0, 0, 256, 1, 1, 1, 256, 256, 128, 32,
+                                         f_ids.data_ptr(), f_lens.data_ptr(), p_ids.data_ptr(), p_lens.data_ptr(),
+                                         None, ws.data_ptr(), ws_bytes, state,
+                                         torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(f_ids.cpu().numpy(), ref.unmasked_kv_ids)
+        assert np.array_equal(p_ids.cpu().numpy(), ref.masked_kv_ids)
+        assert np.array_equal(f_lens.cpu().numpy(), ref.unmasked_lens)
+        assert np.array_equal(p_lens.cpu().numpy(), ref.masked_lens)
+    assert int(clean.sum()) == 0
+    ws = clean
     # too small a workspace is refused before any launch
     rc = native_lib.sa_classify_mask(m.data_ptr(), 0, 0, 256, 1, 1, 1, 256, 256, 128, 32,
                                      f_ids.data_ptr(), f_lens.data_ptr(), p_ids.data_ptr(), p_lens.data_ptr(),
-                                     None, ws.data_ptr(), 1, torch.cuda.current_stream().cuda_stream)
+                                     None, ws.data_ptr(), 1, _native.SA_WS_UNKNOWN,
+                                     torch.cuda.current_stream().cuda_stream)
     assert rc == -3

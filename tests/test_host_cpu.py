@@ -32,16 +32,22 @@ def test_argument_validation_needs_no_gpu(native_lib):
     assert native_lib.sa_unique_planes(8, 32, 4096 * 4096, 0, ctypes.byref(bu), ctypes.byref(hu)) == 0
     assert (bu.value, hu.value) == (8, 1)
     assert native_lib.sa_unique_planes(0, 1, 0, 0, ctypes.byref(bu), ctypes.byref(hu)) == -1
-    assert native_lib.sa_classify_workspace_bytes(8, 1, 4096, 4096) == 8 * 128 * 128
+    # headline mask: per (plane, 32-row slice) a 4-byte counter and eight 8-byte words (one per
+    # 512-column strip), rounded up to 256 B
+    assert native_lib.sa_classify_workspace_bytes(8, 1, 4096, 4096) == (8 * 128 * (4 + 8 * 8) + 255) // 256 * 256
+    assert native_lib.sa_classify_workspace_bytes(1, 1, 64, 64) == 256
     # null pointers / non-dividing block sizes are rejected before anything is launched
     assert native_lib.sa_classify_mask(None, 0, 0, 64, 1, 1, 1, 64, 64, 32, 32, None, None, None, None, None,
-                                       None, 0, None) == -1
+                                       None, 0, 0, None) == -1
     buf = (ctypes.c_uint8 * 64)()
     p = ctypes.addressof(buf)
     p -= p % 16
-    assert native_lib.sa_classify_mask(p, 0, 0, 64, 1, 1, 1, 64, 64, 48, 32, p, p, p, p, None, p, 1 << 20, None) == -1
-    assert native_lib.sa_classify_mask(p, 0, 0, 64, 1, 1, 1, 64, 64, 16, 32, p, p, p, p, None, p, 1 << 20, None) == -2
-    assert native_lib.sa_classify_mask(p, 0, 0, 64, 1, 1, 1, 64, 64, 32, 32, p, p, p, p, None, p, 0, None) == -3
+    assert native_lib.sa_classify_mask(p, 0, 0, 64, 1, 1, 1, 64, 64, 48, 32, p, p, p, p, None, p, 1 << 20, 0, None) == -1
+    assert native_lib.sa_classify_mask(p, 0, 0, 64, 1, 1, 1, 64, 64, 16, 32, p, p, p, p, None, p, 1 << 20, 0, None) == -2
+    assert native_lib.sa_classify_mask(p, 0, 0, 64, 1, 1, 1, 64, 64, 32, 32, p, p, p, p, None, p, 0, 0, None) == -3
+    assert native_lib.sa_classify_mask(p, 0, 0, 64, 1, 1, 1, 64, 64, 32, 32, p, p, p, p, None, p, 1 << 20, 7, None) == -1
+    assert native_lib.sa_classify_mask(p, 0, 0, 2048, 1, 1, 1, 2048, 64, 2048, 32, p, p, p, p, None, p, 1 << 20, 0,
+                                       None) == -2     # BLOCK_Q above 1024
 
 
 def test_entry_points_refuse_cpu_tensors(native_lib):

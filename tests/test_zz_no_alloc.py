@@ -34,7 +34,8 @@ def test_static_scratch_entry_matches_workspace_entry(native_lib):
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=DEV)
         rc = native_lib.sa_classify_mask(m.data_ptr(), 0, 0, S, 1, 1, 1, S, S, bq, bk,
                                          want[0].data_ptr(), want[1].data_ptr(), want[2].data_ptr(),
-                                         want[3].data_ptr(), want[4].data_ptr(), ws.data_ptr(), ws_bytes, stream)
+                                         want[3].data_ptr(), want[4].data_ptr(), ws.data_ptr(), ws_bytes,
+                                         0, stream)          # 0: contents unknown, cleared by the call
         assert rc == 0
         got = _outputs(nq, nk, S, 9)
         torch.cuda.synchronize()
@@ -51,12 +52,13 @@ def test_static_scratch_entry_matches_workspace_entry(native_lib):
 
 
 def test_static_scratch_entry_rejects_oversized_masks(native_lib):
-    # 8 planes of 8192 x 8192 need 512 KiB of flags plus counters... 16 planes exceed the 1 MiB array
-    S = 8192
-    need = native_lib.sa_classify_workspace_bytes(32, 1, S, S)
+    # one plane of 32768 x 32768 needs about half of the 1 MiB array; four planes do not fit
+    S = 32768
+    assert native_lib.sa_classify_workspace_bytes(1, 1, S, S) <= (1 << 20)
+    need = native_lib.sa_classify_workspace_bytes(4, 1, S, S)
     assert need > (1 << 20)
     dummy = torch.zeros(64, dtype=torch.int32, device=DEV)
     p = dummy.data_ptr()
-    rc = native_lib.sa_classify_mask_static(p, S * S, 0, S, 1, 32, 1, S, S, 128, 32, p, p, p, p, None,
+    rc = native_lib.sa_classify_mask_static(p, S * S, 0, S, 1, 4, 1, S, S, 128, 32, p, p, p, p, None,
                                             torch.cuda.current_stream().cuda_stream)
     assert rc == -3 and b"workspace" in native_lib.sa_status_str(rc)
