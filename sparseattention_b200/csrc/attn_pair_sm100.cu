@@ -18,11 +18,12 @@
 //              the list, plus the 512-byte bit-mask tiles of the partial blocks (cp.async.bulk from the
 //              packed plane of stage 1); loads the Q tile of each query block.
 //     warp 1   V producer: the same for V.
-//     warp 2   MMA issuer.  S(j) = Q.K(j)^T into the slot's score columns of tensor memory, then -- once
-//              the softmax has replaced the scores by P(j) in the same columns -- O += P(j).V(j), then
-//              S(j+1), ...: one thread issues them in this order, so the product that reads P(j) is ahead
-//              of the product that overwrites it.
-//     warp 3   idle.
+//     warp 2   (of slot 0's helpers; it serves both slots) MMA issuer.  S(j) = Q.K(j)^T into the slot's score
+//              columns of tensor memory, then -- once the softmax has replaced the scores by P(j) in the same
+//              columns -- O += P(j).V(j), then S(j+1), ...: one thread issues them in this order, so the
+//              product that reads P(j) is ahead of the product that overwrites it; a slot's "O += P.V, next S"
+//              pair is issued back to back, and the pairs of the two slots alternate.
+//     others   idle.
 //   per slot, one warpgroup of softmax threads (registers raised to 216 each), a thread per query row:
 //              scores are exponentiated against the row's running reference max in a single pass (base 2,
 //              scale folded as in sparse_attn_kernel.py:152; a row's first scores are tried against 0) and P
@@ -48,6 +49,12 @@
 
 #include "ptx_sm100.cuh"
 #include "sa_common.cuh"
+
+#ifdef SA_SETMAXNREG
+#define SA_COLD __forceinline__
+#else
+#define SA_COLD __noinline__
+#endif
 
 namespace sa {
 namespace {
@@ -136,7 +143,11 @@ __device__ __forceinline__ void softmax_chunk(const uint32_t* r, uint32_t w, uin
       x1 = (w >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
     }
     xmax[i & 1] = ptx::max3(xmax[i & 1], x0, x1);
+#ifdef SA_DBG_NOEXP
+    const float p0 = x0 * 0.001f, p1 = x1 * 0.001f;
+#else
     const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+#endif
     sum2[i & 1] = ptx::add_f32x2(sum2[i & 1], ptx::pack_f32x2(p0, p1));
     pk[i] = Fmt<T>::pack2(p0, p1);
   }
@@ -150,29 +161,38 @@ template <typename T, bool kMasked>
 __device__ __forceinline__ void softmax_pass(uint32_t t_s, float scale, float m_ref, const uint32_t (&w)[4],
                                              uint32_t (&pk)[64], float& sum_out, float& xmax_out) {
   bool dead[4], solid[4];
-  uint32_t r[128];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     dead[c] = kMasked && __all_sync(0xffffffffu, w[c] == 0u);
     solid[c] = !kMasked || __all_sync(0xffffffffu, w[c] == 0xffffffffu);
-    ptx::tmem_ld32(t_s + 32 * c, *reinterpret_cast<uint32_t(*)[32]>(r + 32 * c));
   }
-  ptx::tmem_ld_wait();
   const uint64_t scale2 = ptx::pack_f32x2(scale, scale);
   const uint64_t nm2 = ptx::pack_f32x2(-m_ref, -m_ref);
   uint64_t sum2[2] = {ptx::pack_f32x2(0.f, 0.f), ptx::pack_f32x2(0.f, 0.f)};
   float xmax[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  auto chunk = [&](int c, const uint32_t (&r)[32]) {
     if (dead[c]) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) pk[16 * c + i] = 0u;
     } else if (solid[c]) {
-      softmax_chunk<T, false>(r + 32 * c, w[c], scale2, nm2, pk + 16 * c, sum2, xmax);
+      softmax_chunk<T, false>(r, w[c], scale2, nm2, pk + 16 * c, sum2, xmax);
     } else {
-      softmax_chunk<T, true>(r + 32 * c, w[c], scale2, nm2, pk + 16 * c, sum2, xmax);
+      softmax_chunk<T, true>(r, w[c], scale2, nm2, pk + 16 * c, sum2, xmax);
     }
-  }
+  };
+  // two chunks of scores in registers at a time: the loads of the second half travel while the first
+  // half is exponentiated
+  uint32_t ra[32], rb[32];
+  ptx::tmem_ld32(t_s, ra);
+  ptx::tmem_ld32(t_s + 32, rb);
+  ptx::tmem_ld_wait();
+  chunk(0, ra);
+  ptx::tmem_ld32(t_s + 64, ra);
+  chunk(1, rb);
+  ptx::tmem_ld32(t_s + 96, rb);
+  ptx::tmem_ld_wait();
+  chunk(2, ra);
+  chunk(3, rb);
   float s0, s1;
   ptx::unpack_f32x2(ptx::add_f32x2(sum2[0], sum2[1]), s0, s1);
   sum_out = s0 + s1;
@@ -191,7 +211,7 @@ __device__ __forceinline__ void store_p(uint32_t t_p, const uint32_t (&pk)[64]) 
 // this step's P -- then redoes the pass from the intact scores against m_ref and writes P.  Returns the
 // new row sum.  Called by all lanes of a warp (the tensor-memory accesses are warp-wide).
 template <typename T, int D>
-__device__ __noinline__ float second_pass_cold(uint32_t t_s, uint32_t t_o, float scale, float m_ref, float alpha,
+__device__ SA_COLD float second_pass_cold(uint32_t t_s, uint32_t t_o, float scale, float m_ref, float alpha,
                                                bool rescale_o, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
   if (rescale_o) {
 #pragma unroll 1
@@ -219,7 +239,7 @@ struct TileInfo {
 };
 
 // Out of line: every role calls it once per tile, and one copy keeps the kernel's code small.
-__device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq, int nk, int eps_shift) {
+__device__ SA_COLD TileInfo tile_info(const AttnParams& p, int tile, int nq, int nk, int eps_shift) {
   TileInfo t;
   const int bh = tile / nq;
   t.qblk = tile % nq;
@@ -236,11 +256,16 @@ __device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq
 }
 
 __device__ __forceinline__ void setmaxnreg_dec() {
+#ifdef SA_SETMAXNREG
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
+#endif
 }
 __device__ __forceinline__ void setmaxnreg_inc() {
+#ifdef SA_SETMAXNREG
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+#endif
 }
+
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -365,14 +390,20 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         ptx::mbar_arrive(bar(BAR_TILE_FULL + rs));
       };
       int ord = 0;
+#ifdef SA_DBG_ONESLOT
+      constexpr int kActive = 1;
+      int tile = slot == 0 ? static_cast<int>(blockIdx.x) : n_tiles;
+#else
+      constexpr int kActive = kSlots;
       int tile = static_cast<int>(blockIdx.x) * kSlots + slot;
+#endif
       if (is_k) { if (lane == 0) publish(0, tile); } else { tile = read_tile_warp(0); }
       while (tile < n_tiles && ok) {
         // The next tile is drawn now and published after this one's loads are issued: the answer of
         // the atomic is not waited for until then.
         int drawn = 0;
         if (is_k && lane == 0)
-          drawn = (p.tile_counter != nullptr ? atomicAdd(p.tile_counter, 1) : tile / kSlots * kSlots - static_cast<int>(blockIdx.x) * kSlots + tile % kSlots * 0 + (ord * static_cast<int>(gridDim.x) * kSlots + static_cast<int>(blockIdx.x) * kSlots + slot) - tile + tile / 1) ;
+          drawn = p.tile_counter != nullptr ? atomicAdd(p.tile_counter, 1) : 0;
         const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
         const int b = ti.b, h = ti.h, qblk = ti.qblk, n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps,
                   n_plain = ti.n_plain;
@@ -432,11 +463,18 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
               if (g > 0) ok = ptx::mbar_wait(bar(bar_empty), (g - 1) & 1, abort_flag);
               if (ok && with_bits && u >= kBitStages)
                 ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
+#ifdef SA_DBG_NOLOAD
+              if (ok) { if (g == 0) ptx::mbar_arrive_expect_tx(full_bar, L::kTileBytes); else ptx::mbar_arrive(full_bar); }
+#else
               if (ok) ptx::mbar_arrive_expect_tx(full_bar, tx_bytes);
+#endif
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             int id_c = ids_ring[(j & 3) * 4 + (c_of_lane & 3)];
             if (static_cast<unsigned>(id_c) >= static_cast<unsigned>(nk)) { bad_index = bad_index || has_box; id_c = 0; }
+#ifdef SA_DBG_NOLOAD
+            if (g > 0) continue;
+#endif
             if (ok && has_box)
               ptx::tma_load_4d(s_tile + pnl_of_lane * kPanelBytes + c_of_lane * blk_bytes, tm, full_bar,
                                pnl_of_lane * 64, id_c * p.BK, ch, cb);
@@ -458,8 +496,8 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         ++ord;
         if (is_k) {
           if (lane == 0) {
-            if (p.tile_counter != nullptr) drawn += static_cast<int>(gridDim.x) * kSlots;
-            else drawn = (ord * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x)) * kSlots + slot;
+            if (p.tile_counter != nullptr) drawn += static_cast<int>(gridDim.x) * kActive;
+            else drawn = (ord * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x)) * kActive + slot;
             if (drawn < 0 || drawn > n_tiles) drawn = n_tiles;
             publish(ord, drawn);
           }
@@ -469,72 +507,127 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
           tile = read_tile_warp(ord);
         }
       }
-      if (is_k && lane == 0 && !ok) publish(ord + 1 - 1, n_tiles);   // wake the slot's other roles on the way out
       if (is_k && __any_sync(0xffffffffu, bad_index) && lane == 0 && p.dev_status != nullptr)
         atomicMax(p.dev_status, SA_DEV_BAD_INDEX);
       __syncwarp();
-    } else if (wq == 2) {
-      // ------------------------------------------------------------------ MMA issuer
-      // S(g) = Q.K(g)^T (line 40), then O += P(g).V(g) (line 61) once the softmax has put P(g) where the
-      // scores were, then S(g+1): issued by one thread in this order.
-      constexpr uint32_t idesc_s = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, kTileN, 0);
-      constexpr uint32_t idesc_o = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, D, 1);
-      const uint64_t dq = ptx::umma_desc_sw128(sQ, 16u);
-      const uint32_t dq_lo = static_cast<uint32_t>(dq), d_hi = static_cast<uint32_t>(dq >> 32);
-      const uint32_t dk_lo = static_cast<uint32_t>(ptx::umma_desc_sw128(sK, 16u));
-      const uint64_t dv = ptx::umma_desc_sw128(sV, kPanelBytes);
-      const uint32_t dv_lo = static_cast<uint32_t>(dv), dv_hi = static_cast<uint32_t>(dv >> 32);
-      int g = 0, tq = 0;
-      for (int ord = 0;; ++ord) {
-        const int tile = read_tile_warp(ord);
-        if (tile >= n_tiles) break;
-        const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
-        if (ti.total == 0) continue;
-        bool ok = true;
-        if (lane == 0) {
-          ok = ptx::mbar_wait(bar(BAR_Q_FULL), tq & 1, abort_flag);
-          for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
-            ok = ptx::mbar_wait(bar(BAR_K_FULL), g & 1, abort_flag);
-            if (!ok) break;
-            ptx::tc_fence_after();
+    } else if (warp == 2) {
+      // ------------------------------------------------------------------ MMA issuer (one thread, both slots)
+      // Per slot: S(g) = Q.K(g)^T (line 40), then O += P(g).V(g) (line 61) once the softmax has put P(g)
+      // where the scores were, then S(g+1), ...  One thread issues the products of both slots, a slot's
+      // "O += P.V, next S" pair back to back: the tensor pipe runs them in issue order, so while one
+      // slot's pair executes the other slot's softmax runs, and the two slots settle half a step apart
+      // instead of competing for the tensor pipe and the MUFU at the same moments.  The thread never
+      // blocks on one slot: it polls what each slot needs next.
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, kTileN, 0);
+        constexpr uint32_t idesc_o = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, D, 1);
+        enum Need : int { NEED_TILE, NEED_Q, NEED_S, NEED_PV, FINISHED };
+        struct SlotState {
+          int need, ord, j, g, tq, n_steps;
+          uint32_t bars, tS, tO, dq_lo, dk_lo, dv_lo;
+        } st[kSlots];
+        uint32_t d_hi = 0, dv_hi = 0;
+        for (int s = 0; s < kSlots; ++s) {
+          const uint32_t base_s = sbase + s * L::slot_bytes;
+          const uint64_t dq = ptx::umma_desc_sw128(base_s + L::off_q, 16u);
+          const uint64_t dv = ptx::umma_desc_sw128(base_s + L::off_v, kPanelBytes);
+          d_hi = static_cast<uint32_t>(dq >> 32);
+          dv_hi = static_cast<uint32_t>(dv >> 32);
+          st[s] = SlotState{NEED_TILE, 0, 0, 0, 0, 0,
+                            sbase + L::off_bar + 8u * static_cast<uint32_t>(s * BAR_PER_SLOT),
+                            tmem_base + 256u * s, tmem_base + 256u * s + 128u,
+                            static_cast<uint32_t>(dq),
+                            static_cast<uint32_t>(ptx::umma_desc_sw128(base_s + L::off_k, 16u)),
+                            static_cast<uint32_t>(dv)};
+        }
+        const uint64_t t0 = ptx::global_timer_ns();
+        uint64_t last_progress = t0;
+        uint32_t idle = 0;
+        int finished = 0;
+        while (finished < kSlots) {
+          bool progressed = false;
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              constexpr uint32_t kPanelStep = kPanelBytes >> 4;
-              const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
-              if (kk == 0) ptx::mma_ss_lo<false>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
-              else         ptx::mma_ss_lo<true>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+          for (int s = 0; s < kSlots; ++s) {
+            SlotState& x = st[s];
+            auto sb = [&](int i) { return x.bars + 8u * static_cast<uint32_t>(i); };
+            if (x.need == NEED_TILE) {
+              const int rs = x.ord % kTileRing;
+              if (!ptx::mbar_try_wait(sb(BAR_TILE_FULL + rs), (x.ord / kTileRing) & 1)) continue;
+              const int tile = reinterpret_cast<volatile int*>(smem + s * L::slot_bytes + L::off_ring)[rs];
+              ptx::mbar_arrive(sb(BAR_TILE_EMPTY + rs));
+              progressed = true;
+              if (tile >= n_tiles) { x.need = FINISHED; ++finished; continue; }
+              const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
+              ++x.ord;
+              if (ti.total == 0) continue;
+              x.n_steps = ti.n_steps;
+              x.j = 0;
+              x.need = NEED_Q;
             }
-            ptx::mma_commit(bar(BAR_K_EMPTY));
-            ptx::mma_commit(bar(BAR_S_FULL));
-            ok = ptx::mbar_wait(bar(BAR_P_FULL), g & 1, abort_flag);
-            if (ok) ok = ptx::mbar_wait(bar(BAR_V_FULL), g & 1, abort_flag);
-            // the first product of a tile overwrites O: the previous tile's epilogue must have read it
-            if (ok && j == 0 && tq >= 1) ok = ptx::mbar_wait(bar(BAR_O_FREE), (tq - 1) & 1, abort_flag);
-            if (!ok) break;
-            ptx::tc_fence_after();
-            if (j == 0) {
+            if (x.need == NEED_Q) {
+              if (!ptx::mbar_try_wait(sb(BAR_Q_FULL), x.tq & 1)) continue;
+              x.need = NEED_S;
+              progressed = true;
+            }
+            if (x.need == NEED_PV) {
+              if (!ptx::mbar_try_wait(sb(BAR_P_FULL), x.g & 1)) continue;
+              if (!ptx::mbar_try_wait(sb(BAR_V_FULL), x.g & 1)) continue;
+              // the first product of a tile overwrites O: the previous tile's epilogue must have read it
+              if (x.j == 0 && x.tq >= 1 && !ptx::mbar_try_wait(sb(BAR_O_FREE), (x.tq - 1) & 1)) continue;
+              ptx::tc_fence_after();
+              if (x.j == 0) {
 #pragma unroll
-              for (int kk = 0; kk < kTileN / 16; ++kk) {
-                if (kk == 0) ptx::mma_ts_lo<false>(tO, tS + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
-                else         ptx::mma_ts_lo<true>(tO, tS + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+                for (int kk = 0; kk < kTileN / 16; ++kk) {
+                  if (kk == 0) ptx::mma_ts_lo<false>(x.tO, x.tS + kk * 8u, x.dv_lo + kk * 128u, dv_hi, idesc_o);
+                  else         ptx::mma_ts_lo<true>(x.tO, x.tS + kk * 8u, x.dv_lo + kk * 128u, dv_hi, idesc_o);
+                }
+              } else {
+#pragma unroll
+                for (int kk = 0; kk < kTileN / 16; ++kk)
+                  ptx::mma_ts_lo<true>(x.tO, x.tS + kk * 8u, x.dv_lo + kk * 128u, dv_hi, idesc_o);
               }
-            } else {
-#pragma unroll
-              for (int kk = 0; kk < kTileN / 16; ++kk)
-                ptx::mma_ts_lo<true>(tO, tS + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+              ptx::mma_commit(sb(BAR_V_EMPTY));
+              ++x.j;
+              ++x.g;
+              progressed = true;
+              if (x.j == x.n_steps) {
+                ptx::mma_commit(sb(BAR_O_FULL));
+                ++x.tq;
+                x.need = NEED_TILE;
+                continue;
+              }
+              x.need = NEED_S;
             }
-            ptx::mma_commit(bar(BAR_V_EMPTY));
-            if (j == ti.n_steps - 1) ptx::mma_commit(bar(BAR_O_FULL));
+            if (x.need == NEED_S) {
+              if (!ptx::mbar_try_wait(sb(BAR_K_FULL), x.g & 1)) continue;
+              ptx::tc_fence_after();
+#pragma unroll
+              for (int kk = 0; kk < D / 16; ++kk) {
+                constexpr uint32_t kPanelStep = kPanelBytes >> 4;
+                const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
+                if (kk == 0) ptx::mma_ss_lo<false>(x.tS, x.dq_lo + off, x.dk_lo + off, d_hi, idesc_s);
+                else         ptx::mma_ss_lo<true>(x.tS, x.dq_lo + off, x.dk_lo + off, d_hi, idesc_s);
+              }
+              ptx::mma_commit(sb(BAR_K_EMPTY));
+              ptx::mma_commit(sb(BAR_S_FULL));
+              x.need = NEED_PV;
+              progressed = true;
+            }
+          }
+          // bounded: no progress on either slot for the wait limit (or another role gave up) ends the loop
+          if (progressed) {
+            idle = 0;
+          } else if ((++idle & 0x3ffu) == 0u) {
+            const uint64_t now = ptx::global_timer_ns();
+            if (idle == 0x400u) last_progress = now;
+            if (*abort_flag != 0) break;
+            if (now - last_progress > ptx::kWaitLimitNs) { *abort_flag = 1; break; }
           }
         }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        g = __shfl_sync(0xffffffffu, g, 0);
-        if (!ok) break;
-        ++tq;
       }
       __syncwarp();
     }
-    // warp 3 of a helper warpgroup has nothing to do
+    // the other warps of the helper warpgroups have nothing to do
   } else {
     setmaxnreg_inc();
     // ------------------------------------------------------------------ softmax: thread = query row
@@ -544,7 +637,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
     const float scale = p.scale_log2;
     int g = 0, gu = 0, tq = 0;
     bool staged = false;                             // a staged O tile's stores are in flight
-    if (warp == 2 * 4 * 1 + 0 * 0 + (kSlots * 4) - 8 + slot * 4 && lane == 0) ptx::prefetch_tensormap(&tm_o);
+    if (wq == 0 && lane == 0) ptx::prefetch_tensormap(&tm_o);
     // The stores of the previous tile have had the tile-info loads to read their shared-memory source; the
     // producer may then load the next Q tile into the slot.
     auto release_staged = [&]() {
@@ -580,6 +673,13 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_S_FULL), g & 1, abort_flag));
         if (!ok) break;
         ptx::tc_fence_after();
+#ifdef SA_DBG_NOSOFTMAX
+        if (j >= n_plain) { __syncwarp(); if (lane == 0) ptx::mbar_arrive(bar(BAR_BITS_EMPTY + (gu + (j - n_plain)) % kBitStages)); }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar(BAR_P_FULL));
+        continue;
+#endif
         const bool masked = j >= n_plain;
         uint32_t w[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
         if (masked) {
@@ -756,7 +856,11 @@ int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& m
   });
   if (attr_result[info->ordinal] != cudaSuccess) return SA_ERR_CUDA;
   const int n_tiles = (p.Sq / kTileM) * p.B * p.H;
+#ifdef SA_DBG_ONESLOT
+  const int want = n_tiles;
+#else
   const int want = (n_tiles + kSlots - 1) / kSlots;
+#endif
   const int grid = want < info->sm_count ? want : info->sm_count;    // persistent: one CTA per SM walks the tiles
   if (p.tile_counter != nullptr && cudaMemsetAsync(p.tile_counter, 0, sizeof(int32_t), stream) != cudaSuccess)
     return SA_ERR_CUDA;
@@ -766,7 +870,7 @@ int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& m
 
 }  // namespace
 
-int attn_tc_supported(const AttnParams& p) {
+int attn_tc2_supported(const AttnParams& p) {
   if (p.dtype != SA_DTYPE_F16 && p.dtype != SA_DTYPE_BF16) return 0;
   if (p.D != 64 && p.D != 128) return 0;
   if (p.BQ != kTileM) return 0;
@@ -781,8 +885,8 @@ int attn_tc_supported(const AttnParams& p) {
   return 1;
 }
 
-int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
-  if (!attn_tc_supported(p)) return SA_ERR_UNSUPPORTED;
+int launch_attn_tc2(const AttnParams& p, cudaStream_t stream) {
+  if (!attn_tc2_supported(p)) return SA_ERR_UNSUPPORTED;
   CUtensorMap mq, mk, mv, mo;
   if (!make_map(&mq, p.q, p.dtype, p.B, p.H, p.Sq, p.D, p.qs, kTileM)) return SA_ERR_CUDA;
   if (!make_map(&mk, p.k, p.dtype, p.B, p.H, p.Sk, p.D, p.ks, p.BK)) return SA_ERR_CUDA;

@@ -46,7 +46,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // has given up), records that in *abort_flag (shared memory) and returns false.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 // The polling loop is out of line: a kernel has dozens of waits, and most find the phase complete.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef SA_SETMAXNREG
+static __device__ __forceinline__
+#else
+static __device__ __noinline__
+#endif
+bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
