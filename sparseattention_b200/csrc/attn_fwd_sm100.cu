@@ -3,7 +3,7 @@
 // Replaces sparseattention/sparse_attn_kernel.py:72-146 (kernel) and 10-63 (inner loop)
 // for fp16 / bf16, head dim 64 or 128, BLOCK_Q = 128 and BLOCK_K in {32, 64, 128}.
 //
-// Persistent grid: one CTA per SM (256 threads) works through (query block, batch, head) tiles drawn
+// Persistent grid: one CTA per SM (384 threads) works through (query block, batch, head) tiles drawn
 // from a device-wide counter (tiles differ in length); the loads and first MMAs of a tile overlap the
 // epilogue of the previous one (Q is double-buffered, barrier phases run on across tiles).  For a tile --
 // one query block (128 rows) of one (batch, head) -- the CTA walks its two kv-block lists -- the full list first, then the partial list: the order of
@@ -18,16 +18,15 @@
 //   warp 2     S issuer.  S(j) = Q.K(j)^T into one of two score buffers in tensor memory
 //              (tcgen05.mma, both operands in shared memory), one step ahead of the softmax.
 //   warp 3     P.V issuer.  O += P(j).V(j) with P read from its own buffer in tensor memory.
-//   warps 4-7  softmax; a thread owns a query row (all 128 score columns of a step), so a row's max and
-//              sum never leave its thread.  Scores are exponentiated against the row's running reference
-//              max in a single pass (base 2, scale folded as in sparse_attn_kernel.py:152; a row's first
-//              scores are tried against 0); the reference moves, and the row of O is rescaled in tensor
-//              memory, only when a score exceeds it by more than 2^8 (the pass is then redone from the
-//              scores, which stay intact in their own buffer).  Steps that contain a partial or padding
-//              block apply the bit mask; steps of full blocks do no mask work.  P is rounded to the V
-//              dtype (line 61); row sums stay in fp32 (line 57).  Finally O / l is staged in the tile's Q
-//              slot and written with TMA stores; a row with no attended key yields 0 (the reference
-//              yields NaN, line 53).
+//   warps 4-11 softmax; a thread owns a query row and one half of the 128 score columns.  Scores
+//              are exponentiated against the row's running reference max in a single pass (base 2,
+//              scale folded as in sparse_attn_kernel.py:152; a row's first scores are tried against
+//              0); the reference moves, and O is rescaled in tensor memory, only when a score
+//              exceeds it by more than 2^8 (the pass is then redone from the intact scores).  Steps that contain a partial or padding block apply
+//              the bit mask; steps of full blocks do no mask work.  P is rounded to the V dtype
+//              (line 61); row sums stay in fp32 (line 57).  Finally O / l is staged in the tile's Q
+//              slot and written with one TMA store per warp; a row with no attended key yields 0
+//              (the reference yields NaN, line 53).
 //
 // Tensor memory (512 columns): score buffers at 0 and 128, O at 256, P buffers at 384 and 448.
 //
@@ -48,9 +47,9 @@ namespace {
 
 constexpr int kTileM = 128;          // query rows per CTA (= BLOCK_Q)
 constexpr int kTileN = 128;          // kv rows per MMA step
-constexpr int kThreadsTC = 256;      // warps: K producer, V producer, S issuer, P.V issuer, 4 softmax
+constexpr int kSplit = 2;            // threads per query row in the softmax (column groups)
+constexpr int kThreadsTC = 128 + 128 * kSplit;   // warps: K producer, V producer, S issuer, P.V issuer, 4 * kSplit softmax
 constexpr int kSoftmaxWarp0 = 4;     // first softmax warp (a multiple of 4: TMEM lane quarter = warp % 4)
-constexpr int kSoftmaxWarps = 4;
 constexpr uint32_t kTmemCols = 512;  // score buffers at columns 0 and 128, O at 256, P buffers at 384 and 448
 constexpr int kStagesK = 2;          // K tiles in flight in shared memory
 constexpr int kStagesV = 2;          // V tiles in flight in shared memory
@@ -59,7 +58,6 @@ constexpr int kTileRing = 4;         // tile indices the scheduling warp may be 
 constexpr uint32_t kPanelBytes = 128u * 128u;   // 128 rows x 64 elements x 2 B
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 constexpr float kFreshFloor = -4.0f;            // a row's first scores are taken against 0 if their max is in [-4, 8]
-
 enum Bar : int {
   BAR_Q_FULL = 0,                                  // 2: Q tile of a query block landed
   BAR_Q_EMPTY = BAR_Q_FULL + 2,                    // 2: last S of the tile that used the Q slot complete
@@ -89,7 +87,8 @@ struct Smem {
   static constexpr uint32_t off_bar = off_bits + kBitStages * 4 * 128 * 4;
   static constexpr uint32_t off_misc = off_bar + 8 * 48;
   static constexpr uint32_t off_ids = off_misc + 16 + 4 * kTileRing;   // misc: TMEM base, abort flag, tile ring
-  static constexpr uint32_t total = off_ids + 2 * 4 * 4 * 4;           // ids: per producer warp [4 steps][4 entries]
+  static constexpr uint32_t off_xch = off_ids + 2 * 4 * 4 * 4;         // ids: per producer warp [4 steps][4 entries]; xch: [2 parities + epilogue][kSplit column groups][128 rows] f32
+  static constexpr uint32_t total = off_xch + 3 * kSplit * 128 * 4;
   static constexpr uint32_t dynamic_bytes = total + 1024;       // slack to align the base to 1024 B
 };
 static_assert(BAR_COUNT <= 48, "barrier area too small");
@@ -117,100 +116,113 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 
-// 32 score columns of one row: x = s*scale - m_ref, masked columns -> -inf (kMasked), P = exp2(x) rounded
-// to T into pk, fp32 sum of the unrounded P (lines 54, 57, 61) and max of x.  Two independent accumulator
-// pairs, so that consecutive pairs of columns do not wait for one another's result.
+// 32 score columns of one thread: x = s*scale - m_ref, masked columns -> -inf (kMasked), P = exp2(x)
+// rounded to T into pk, fp32 sum of the unrounded P (lines 54, 57, 61) and max of x.
+// The running max and sum are kept in kAcc independent accumulators each (pair i goes to i % kAcc), so
+// that consecutive pairs do not wait for one another's result.
+constexpr int kAcc = 2;
 template <typename T, bool kMasked>
 __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t w, uint64_t scale2, uint64_t nm2,
-                                              uint32_t (&pk)[16], uint64_t (&sum2)[2], float (&xmax)[2]) {
+                                              uint32_t (&pk)[16], uint64_t (&sum2v)[kAcc], float (&xmaxv)[kAcc]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
+    uint64_t& sum2 = sum2v[i % kAcc];
+    float& xmax = xmaxv[i % kAcc];
     float x0, x1;
     ptx::unpack_f32x2(ptx::fma_f32x2(ptx::pack_u32x2(r[2 * i], r[2 * i + 1]), scale2, nm2), x0, x1);
     if (kMasked) {
       x0 = (w >> (2 * i)) & 1u ? x0 : -INFINITY;                 // line 47
       x1 = (w >> (2 * i + 1)) & 1u ? x1 : -INFINITY;
     }
-    xmax[i & 1] = ptx::max3(xmax[i & 1], x0, x1);
+    xmax = ptx::max3(xmax, x0, x1);
     const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-    sum2[i & 1] = ptx::add_f32x2(sum2[i & 1], ptx::pack_f32x2(p0, p1));
+    sum2 = ptx::add_f32x2(sum2, ptx::pack_f32x2(p0, p1));
     pk[i] = Fmt<T>::pack2(p0, p1);
   }
 }
 
-// One pass over the 128 scores of this thread's row, in four chunks of 32 (on masked steps a chunk is one
-// 32 x 32 block of the mask for the warp's 32 rows, w[c] its word for this row).  A block that is False for
-// all 32 rows costs no arithmetic (P = 0, no exponentials); one that is True for all 32 rows takes the
-// mask-free arithmetic.  Two chunks of scores are in registers at a time: the loads of the second half
-// travel while the first half is exponentiated; P goes to its buffer chunk by chunk.
-template <typename T, bool kMasked>
+// One pass over this thread's kCW score columns, kCW / 32 chunks of 32.  w[c] is the bit-mask word
+// of chunk c for this thread's row; a warp covers 32 rows, so on masked steps a chunk is one 32 x 32
+// block of the mask.  A block that is False for all 32 rows costs no arithmetic (P = 0, no
+// exponentials); one that is True for all 32 rows takes the mask-free arithmetic.
+template <typename T, bool kMasked, int kCW>
 __device__ __forceinline__ void softmax_pass(uint32_t t_s, uint32_t t_p, float scale, float m_ref,
-                                             const uint32_t (&w)[4], float& sum_out, float& xmax_out) {
-  bool dead[4], solid[4];
+                                             const uint32_t (&w)[kCW / 32], float& sum_out, float& xmax_out) {
+  constexpr int kChunks = kCW / 32;
+  bool dead[kChunks], solid[kChunks];
+  uint32_t r[kChunks][32];
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < kChunks; ++c) {
     dead[c] = kMasked && __all_sync(0xffffffffu, w[c] == 0u);
     solid[c] = !kMasked || __all_sync(0xffffffffu, w[c] == 0xffffffffu);
+    ptx::tmem_ld32(t_s + 32 * c, r[c]);
   }
+  ptx::tmem_ld_wait();
   const uint64_t scale2 = ptx::pack_f32x2(scale, scale);
   const uint64_t nm2 = ptx::pack_f32x2(-m_ref, -m_ref);
-  uint64_t sum2[2] = {ptx::pack_f32x2(0.f, 0.f), ptx::pack_f32x2(0.f, 0.f)};
-  float xmax[2] = {-INFINITY, -INFINITY};
-  auto chunk = [&](int c, const uint32_t (&r)[32]) {
+  uint64_t sum2[kAcc];
+  float xmax[kAcc];
+#pragma unroll
+  for (int a = 0; a < kAcc; ++a) { sum2[a] = ptx::pack_f32x2(0.f, 0.f); xmax[a] = -INFINITY; }
+#pragma unroll
+  for (int c = 0; c < kChunks; ++c) {
     uint32_t pk[16];
     if (dead[c]) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) pk[i] = 0u;
     } else if (solid[c]) {
-      softmax_chunk<T, false>(r, w[c], scale2, nm2, pk, sum2, xmax);
+      softmax_chunk<T, false>(r[c], w[c], scale2, nm2, pk, sum2, xmax);
     } else {
-      softmax_chunk<T, true>(r, w[c], scale2, nm2, pk, sum2, xmax);
+      softmax_chunk<T, true>(r[c], w[c], scale2, nm2, pk, sum2, xmax);
     }
     ptx::tmem_st16(t_p + 16 * c, pk);
-  };
-  uint32_t ra[32], rb[32];
-  ptx::tmem_ld32(t_s, ra);
-  ptx::tmem_ld32(t_s + 32, rb);
-  ptx::tmem_ld_wait();
-  chunk(0, ra);
-  ptx::tmem_ld32(t_s + 64, ra);
-  chunk(1, rb);
-  ptx::tmem_ld32(t_s + 96, rb);
-  ptx::tmem_ld_wait();
-  chunk(2, ra);
-  chunk(3, rb);
+  }
+#pragma unroll
+  for (int a = 1; a < kAcc; ++a) { sum2[0] = ptx::add_f32x2(sum2[0], sum2[a]); xmax[0] = fmaxf(xmax[0], xmax[a]); }
   float s0, s1;
-  ptx::unpack_f32x2(ptx::add_f32x2(sum2[0], sum2[1]), s0, s1);
+  ptx::unpack_f32x2(sum2[0], s0, s1);
   sum_out = s0 + s1;
-  xmax_out = fmaxf(xmax[0], xmax[1]);
+  xmax_out = xmax[0];
 }
 
-// The rare second pass of a step, after the reference max of some row of the warp moved, out of line so
-// that the hot loop stays small: rescales this thread's row of O by alpha (sparse_attn_kernel.py:58) when
-// asked to, then redoes the pass from the intact scores against m_ref.  Returns the new row sum.  Called
-// by all lanes of a warp (the tensor-memory accesses are warp-wide).
-template <typename T, int D>
+// Moves kCols fp32 columns between tensor memory and registers (kCols = 32 or 16).
+template <int kCols>
+__device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&r)[kCols]) {
+  if constexpr (kCols == 32) ptx::tmem_ld32(taddr, r); else ptx::tmem_ld16(taddr, r);
+}
+template <int kCols>
+__device__ __forceinline__ void tmem_store_cols(uint32_t taddr, const uint32_t (&r)[kCols]) {
+  if constexpr (kCols == 32) ptx::tmem_st32(taddr, r); else ptx::tmem_st16(taddr, r);
+}
+
+// The rare second pass of a step, after the reference max of some row moved, out of line so that the
+// hot loop stays small: rescales this thread's O columns by alpha (sparse_attn_kernel.py:58) when
+// asked to, then redoes the pass from the intact scores against m_ref.  Returns the new row sum.
+template <typename T, int kCW, int kOC>
 __device__ __noinline__ float second_pass_cold(uint32_t t_s, uint32_t t_p, uint32_t t_o, float scale, float m_ref,
                                                float alpha, bool rescale_o, uint32_t pv_bar, uint32_t pv_parity,
-                                               volatile int* abort_flag, uint32_t w0, uint32_t w1, uint32_t w2,
-                                               uint32_t w3) {
+                                               volatile int* abort_flag, uint32_t w0, uint32_t w1) {
+  constexpr int kOChunk = kOC > 32 ? 32 : kOC;
   if (rescale_o) {
     // O must hold every product up to the previous step before it is rescaled.
     ptx::mbar_wait(pv_bar, pv_parity, abort_flag);
     ptx::tc_fence_after();
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
-      uint32_t r[32];
-      ptx::tmem_ld32(t_o + 32 * c, r);
+    for (int c = 0; c < kOC / kOChunk; ++c) {
+      uint32_t r[kOChunk];
+      tmem_load_cols<kOChunk>(t_o + c * kOChunk, r);
       ptx::tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-      ptx::tmem_st32(t_o + 32 * c, r);
+      for (int i = 0; i < kOChunk; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+      tmem_store_cols<kOChunk>(t_o + c * kOChunk, r);
     }
   }
-  const uint32_t w[4] = {w0, w1, w2, w3};
+  static_assert(kCW / 32 <= 2, "the out-of-line pass takes two mask words");
+  uint32_t w[kCW / 32];
+  w[0] = w0;
+  if (kCW / 32 > 1) w[kCW / 32 - 1] = w1;
   float sum, xmax;
-  softmax_pass<T, true>(t_s, t_p, scale, m_ref, w, sum, xmax);
+  softmax_pass<T, true, kCW>(t_s, t_p, scale, m_ref, w, sum, xmax);
   return sum;
 }
 
@@ -256,8 +268,12 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::off_misc);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::off_misc + 4);
   volatile int* tile_ring = reinterpret_cast<volatile int*>(smem + L::off_misc + 16);
+  float* xch = reinterpret_cast<float*>(smem + L::off_xch);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The epilogue stages a tile of O in the Q slot it has finished with and stores it with TMA when a
+  // thread's share of a row is one 128-byte swizzle row; otherwise the threads store their rows directly.
+  constexpr bool kStageO = (D / kSplit) * sizeof(T) == 128;
   const int nq = p.Sq / kTileM;
   const int nk = p.Sk / p.BK;
   // BLOCK_K is 32, 64 or 128: list entries per step (4, 2, 1) and 32-column sub-slots per entry
@@ -271,9 +287,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       ptx::mbar_init(bar(BAR_Q_FULL + i), 1);
       ptx::mbar_init(bar(BAR_Q_EMPTY + i), 1);
       ptx::mbar_init(bar(BAR_S_FULL + i), 1);
-      ptx::mbar_init(bar(BAR_P_FULL + i), kSoftmaxWarps);      // one arrival per softmax warp
+      ptx::mbar_init(bar(BAR_P_FULL + i), 4 * kSplit);      // one arrival per softmax warp
       ptx::mbar_init(bar(BAR_PV_DONE + i), 1);
-      ptx::mbar_init(bar(BAR_Q_STORED + i), kSoftmaxWarps);
+      ptx::mbar_init(bar(BAR_Q_STORED + i), 4 * kSplit);
     }
     for (int i = 0; i < kStagesK; ++i) {
       ptx::mbar_init(bar(BAR_K_FULL + i), 1);
@@ -284,13 +300,13 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       ptx::mbar_init(bar(BAR_V_EMPTY + i), 1);
     }
     ptx::mbar_init(bar(BAR_O_FULL), 1);
-    ptx::mbar_init(bar(BAR_O_FREE), kSoftmaxWarps);
+    ptx::mbar_init(bar(BAR_O_FREE), 4 * kSplit);
     for (int i = 0; i < kBitStages; ++i) {
-      ptx::mbar_init(bar(BAR_BITS_EMPTY + i), kSoftmaxWarps);
+      ptx::mbar_init(bar(BAR_BITS_EMPTY + i), 4 * kSplit);
     }
     for (int i = 0; i < kTileRing; ++i) {
       ptx::mbar_init(bar(BAR_TILE_FULL + i), 1);
-      ptx::mbar_init(bar(BAR_TILE_EMPTY + i), 3 + kSoftmaxWarps);    // V producer, two issuers, softmax warps
+      ptx::mbar_init(bar(BAR_TILE_EMPTY + i), 3 + 4 * kSplit);    // V producer, two issuers, softmax warps
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -376,7 +392,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         if (lane == 0) {
           if (tq >= 2) {
             ok = ptx::mbar_wait(bar(BAR_Q_EMPTY + qs), ((tq >> 1) - 1) & 1, abort_flag);
-            if (ok) ok = ptx::mbar_wait(bar(BAR_Q_STORED + qs), ((tq >> 1) - 1) & 1, abort_flag);
+            if (ok && kStageO) ok = ptx::mbar_wait(bar(BAR_Q_STORED + qs), ((tq >> 1) - 1) & 1, abort_flag);
           }
           if (ok) {
             const int qb = p.qs[0] ? b : 0, qh = p.qs[1] ? h : 0;
@@ -559,20 +575,26 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ softmax: thread = query row
-    // A warp may only touch the TMEM lanes of its quarter (warp % 4).
+    // ------------------------------------------------------------------ softmax
+    // Thread = (query row, one of kSplit groups of 128 / kSplit score columns): the first four
+    // softmax warps take the first group, the next four the second, ...; a warp may only touch the
+    // TMEM lanes of its quarter (warp % 4).  A group is kCW / 32 sub-slots, one bit-mask word each.
+    constexpr int kCW = kTileN / kSplit;           // score columns per thread
+    constexpr int kOC = D / kSplit;                // O columns this thread rescales and stores
+    constexpr int kOChunk = kOC > 32 ? 32 : kOC;
     const int lq = warp & 3;
+    const int quarter = (warp - kSoftmaxWarp0) >> 2;
     const int row = lq * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(lq * 32) << 16;
-    const uint32_t tO_mine = tO + lane_off;
+    const uint32_t tO_mine = tO + lane_off + kOC * quarter;
     const float scale = p.scale_log2;
     int g0 = 0, gu = 0, tq = 0;
-    int stored_slot = -1;                          // Q slot holding a staged O tile whose stores are in flight
-    if (warp == kSoftmaxWarp0 && lane == 0) ptx::prefetch_tensormap(&tm_o);
-    // The stores of the previous tile have had the tile-info loads to read their shared-memory source; the
+    int stored_slot = -1;                          // Q slot holding a staged O tile whose store is in flight
+    if (kStageO && warp == kSoftmaxWarp0 && lane == 0) ptx::prefetch_tensormap(&tm_o);
+    // The store of the previous tile has had the tile-info loads to read its shared-memory source; the
     // producer may then reuse the slot for the Q tile after next.
     auto release_staged = [&]() {
-      if (stored_slot >= 0) {
+      if (kStageO && stored_slot >= 0) {
         if (lane == 0) {
           ptx::bulk_wait_group_read0();
           ptx::mbar_arrive(bar(BAR_Q_STORED + stored_slot));
@@ -580,25 +602,25 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         stored_slot = -1;
       }
     };
-    bool ok = true;
-    for (int ord = 0; ok; ++ord) {
+    for (int ord = 0;; ++ord) {
       const int tile = next_tile_warp(ord);
       if (tile >= n_tiles) break;
       const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
       const int n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps, n_plain = ti.n_plain;
       release_staged();
+      T* o_base = static_cast<T*>(p.o) + ti.b * p.os[0] + ti.h * p.os[1] +
+                  static_cast<int64_t>(ti.qblk) * kTileM * p.os[2];
+      uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + kOC * quarter);
       float* lse_row = p.lse == nullptr ? nullptr
           : p.lse + (static_cast<int64_t>(ti.b) * p.H + ti.h) * p.Sq + ti.qblk * kTileM + row;
       if (total == 0) {                            // nothing attended: the rows are 0
-        T* o_row = static_cast<T*>(p.o) + ti.b * p.os[0] + ti.h * p.os[1] +
-                   (static_cast<int64_t>(ti.qblk) * kTileM + row) * p.os[2];
-        uint4* dst = reinterpret_cast<uint4*>(o_row);
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (lse_row != nullptr) *lse_row = -INFINITY;
+        for (int i = 0; i < kOC / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (lse_row != nullptr && quarter == 0) *lse_row = -INFINITY;
         continue;
       }
-      float m = -INFINITY, l = 0.f;                // lines 103-104
+      float m = -INFINITY, l = 0.f;                // lines 103-104; l holds this group's partial sum
+      bool gave_up = false;
       for (int j = 0; j < n_steps; ++j) {
         const int g = g0 + j;                      // steps since the kernel started: buffer and phase
         {
@@ -611,26 +633,44 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
           bool mine = true;
           if (!ok_s) mine = ptx::mbar_wait_slow(b_s, par_s, abort_flag);
           if (!ok_pv) mine = ptx::mbar_wait_slow(b_pv, par_pv, abort_flag) && mine;
-          ok = __all_sync(0xffffffffu, mine);      // the whole warp leaves together (warp-wide TMEM accesses follow)
-          if (!ok) break;
+          // A failed wait (it ran out, or another thread's did) ends the role.  The warp leaves as a whole
+          // (warp-wide tensor-memory accesses follow), and it first arrives on the barrier on which the
+          // other warp of its rows may be waiting for this step's exchange; that warp finds the abort flag
+          // set when it wakes and leaves too.
+          if (!__all_sync(0xffffffffu, mine)) {
+            ptx::named_bar_arrive(1 + lq, 32 * kSplit);
+            gave_up = true;
+            break;
+          }
         }
         ptx::tc_fence_after();
-        // this row's scores of buffer g & 1, and where its P goes
-        const uint32_t tS_mine = tmem_base + 128u * (g & 1) + lane_off;
-        const uint32_t tP_mine = tmem_base + 384u + 64u * (g & 1) + lane_off;
+        // this group's scores of buffer g & 1, and where its P goes
+        const uint32_t tS_mine = tmem_base + 128u * (g & 1) + lane_off + kCW * quarter;
+        const uint32_t tP_mine = tmem_base + 384u + 64u * (g & 1) + lane_off + (kCW / 2) * quarter;
         const bool masked = j >= n_plain;
-        uint32_t w[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        uint32_t w[kCW / 32];
+#pragma unroll
+        for (int c = 0; c < kCW / 32; ++c) w[c] = 0xffffffffu;
         if (masked) {
           const int u = gu + (j - n_plain), st = u % kBitStages;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int e = (j << eps_shift) + (c >> sps_shift);
-            const uint32_t word = bits_smem[(st * 4 + c) * 128 + row];    // stale for a full or padding slot
+          for (int c = 0; c < kCW / 32; ++c) {
+            const int ss = quarter * (kCW / 32) + c;           // sub-slot of the step
+            const int e = (j << eps_shift) + (ss >> sps_shift);
+            const uint32_t word = bits_smem[(st * 4 + ss) * 128 + row];    // stale for a full or padding slot
             w[c] = e < n_full ? 0xffffffffu : (e < total ? word : 0u);
           }
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar(BAR_BITS_EMPTY + st));
         }
+        float* xch_mine = xch + ((g & 1) * kSplit + quarter) * 128 + row;
+        const float* xch_row = xch + (g & 1) * kSplit * 128 + row;
+        auto row_max = [&]() {
+          float v = xch_row[0];
+#pragma unroll
+          for (int q = 1; q < kSplit; ++q) v = fmaxf(v, xch_row[128 * q]);
+          return v;
+        };
 
         // One pass against the row's running reference max; a row that has accumulated nothing yet is
         // tried against 0.  The reference only moves (and the pass is redone from the intact scores)
@@ -642,9 +682,13 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         float m_new = m, alpha = 1.f;
         bool second_pass = true;
         {
-          float sum, xrow;
-          if (masked) softmax_pass<T, true>(tS_mine, tP_mine, scale, m_try, w, sum, xrow);
-          else        softmax_pass<T, false>(tS_mine, tP_mine, scale, m_try, w, sum, xrow);
+          float sum, xmax;
+          if (masked) softmax_pass<T, true, kCW>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
+          else        softmax_pass<T, false, kCW>(tS_mine, tP_mine, scale, m_try, w, sum, xmax);
+          *xch_mine = xmax;
+          ptx::named_bar_sync(1 + lq, 32 * kSplit);
+          if (*abort_flag != 0) { gave_up = true; break; }
+          const float xrow = row_max();
           const bool seen = xrow > -INFINITY;
           const bool moved = xrow > kRescaleThreshold || (fresh && seen && xrow < kFreshFloor);
           if (!__any_sync(0xffffffffu, moved)) {
@@ -662,9 +706,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
           // This step waited for P.V(g-2) and the previous one for P.V(g-3): the barrier of step g-1 is at
           // most one phase behind.
           const bool rescale_o = j > 0 && __any_sync(0xffffffffu, alpha != 1.f);
-          const float sum = second_pass_cold<T, D>(
+          const float sum = second_pass_cold<T, kCW, kOC>(
               tS_mine, tP_mine, tO_mine, scale, m_new == -INFINITY ? 0.f : m_new, alpha, rescale_o,
-              bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag, w[0], w[1], w[2], w[3]);
+              bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag, w[0], w[kCW / 32 - 1]);
           l = l * alpha + sum;                                      // line 57
           m = m_new;                                                // line 56
         }
@@ -673,52 +717,71 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar(BAR_P_FULL + (g & 1)));    // one arrival per softmax warp
       }
-      if (!ok) break;
-      // ---- epilogue of the tile: O / l
-      ok = __all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_O_FULL), tq & 1, abort_flag));
-      if (!ok) break;
+      // ---- epilogue of the tile: O / l.  The row sums of the column groups meet in a buffer of their
+      // own (the per-step exchange buffers may already be in use by the next tile's first step).
+      if (gave_up) break;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_O_FULL), tq & 1, abort_flag))) {
+        ptx::named_bar_arrive(1 + lq, 32 * kSplit);
+        break;
+      }
       ptx::tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;                    // line 144, with 0 for an empty row
-      if (lse_row != nullptr)                      // m and l are in base 2 (scale folded, line 152)
-        *lse_row = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
-      // This warp's 32 rows go to a 4 KB slab per 64-column panel of the tile's Q slot (every MMA that read
-      // Q completed before O did) in the 128-byte swizzle, then to global memory as one TMA box per panel.
-      const int qs = tq & 1;
+      float* xl = xch + 2 * kSplit * 128;
+      xl[quarter * 128 + row] = l;
+      ptx::named_bar_sync(1 + lq, 32 * kSplit);
+      if (*abort_flag != 0) break;                 // the other warp of these rows gave up and only arrived
+      float l_row = xl[row];
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld32(tO_mine + 32 * c, r);
+      for (int q = 1; q < kSplit; ++q) l_row += xl[128 * q + row];
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;            // line 144, with 0 for an empty row
+      if (lse_row != nullptr && quarter == 0)      // m and l are in base 2 (scale folded, line 152)
+        *lse_row = l_row > 0.f ? (m + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
+      uint32_t ro[kOC];
+#pragma unroll
+      for (int c = 0; c < kOC / kOChunk; ++c) {
+        uint32_t r[kOChunk];
+        tmem_load_cols<kOChunk>(tO_mine + c * kOChunk, r);
         ptx::tmem_ld_wait();
-        if (c == D / 32 - 1) {
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(bar(BAR_O_FREE));         // O may be overwritten by the next tile
-        }
-        const uint32_t slab = sQ + qs * L::kTileBytes + static_cast<uint32_t>(c / 2) * kPanelBytes +
-                              static_cast<uint32_t>(lq) * 4096u;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int unit = (c & 1) * 4 + i;
-          const uint32_t a = slab + lane * 128u + (static_cast<uint32_t>(unit ^ (lane & 7)) << 4);
-          ptx::st_shared_v4(a,
-              Fmt<T>::pack2(__uint_as_float(r[8 * i + 0]) * inv, __uint_as_float(r[8 * i + 1]) * inv),
-              Fmt<T>::pack2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv),
-              Fmt<T>::pack2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv),
-              Fmt<T>::pack2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv));
-        }
+        for (int i = 0; i < kOChunk; ++i) ro[c * kOChunk + i] = r[i];
       }
-      ptx::fence_proxy_async();
+      ptx::tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        if (*abort_flag == 0) {                    // a wait that ran out leaves the flag set; nothing is written then
+      if (lane == 0) ptx::mbar_arrive(bar(BAR_O_FREE));             // O may be overwritten by the next tile
+      // A wait that ran out leaves the abort flag set; nothing is written in that case.
+      if constexpr (kStageO) {
+        // This warp's 32 rows x 128 bytes go to a 4 KB slab of the tile's Q slot (every MMA that read Q
+        // completed before O did) in the 128-byte swizzle, then to global memory as one TMA box.
+        const int qs = tq & 1;
+        const uint32_t slab = sQ + qs * L::kTileBytes + static_cast<uint32_t>(quarter * 4 + lq) * 4096u;
+        const bool live = *abort_flag == 0;
 #pragma unroll
-          for (int pnl = 0; pnl < D / 64; ++pnl)
-            ptx::tma_store_4d(&tm_o, sQ + qs * L::kTileBytes + pnl * kPanelBytes + static_cast<uint32_t>(lq) * 4096u,
-                              64 * pnl, ti.qblk * kTileM + lq * 32, p.os[1] ? ti.h : 0, p.os[0] ? ti.b : 0);   // line 146
+        for (int i = 0; i < kOC / 8; ++i) {
+          const uint32_t a = slab + lane * 128u + (static_cast<uint32_t>(i ^ (lane & 7)) << 4);
+          ptx::st_shared_v4(a,
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 0]) * inv, __uint_as_float(ro[8 * i + 1]) * inv),
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 2]) * inv, __uint_as_float(ro[8 * i + 3]) * inv),
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 4]) * inv, __uint_as_float(ro[8 * i + 5]) * inv),
+              Fmt<T>::pack2(__uint_as_float(ro[8 * i + 6]) * inv, __uint_as_float(ro[8 * i + 7]) * inv));
         }
-        ptx::bulk_commit_group();
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0 && live) {
+          ptx::tma_store_4d(&tm_o, slab, kOC * quarter, ti.qblk * kTileM + lq * 32, p.os[1] ? ti.h : 0,
+                            p.os[0] ? ti.b : 0);                                      // line 146
+          ptx::bulk_commit_group();
+        }
+        stored_slot = qs;
+      } else if (*abort_flag == 0) {
+#pragma unroll
+        for (int i = 0; i < kOC / 8; ++i) {
+          uint4 v;
+          v.x = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 0]) * inv, __uint_as_float(ro[8 * i + 1]) * inv);
+          v.y = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 2]) * inv, __uint_as_float(ro[8 * i + 3]) * inv);
+          v.z = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 4]) * inv, __uint_as_float(ro[8 * i + 5]) * inv);
+          v.w = Fmt<T>::pack2(__uint_as_float(ro[8 * i + 6]) * inv, __uint_as_float(ro[8 * i + 7]) * inv);
+          dst[i] = v;                                               // line 146
+        }
       }
-      stored_slot = qs;
       g0 += n_steps;
       gu += n_steps - n_plain;
       ++tq;
@@ -776,12 +839,11 @@ bool make_map(CUtensorMap* out, const void* base, int dtype, int B, int H, int S
   return r == CUDA_SUCCESS;
 }
 
-bool tma_friendly(const void* base, const int64_t* st, int S) {
+bool tma_friendly(const void* base, const int64_t* st) {
   if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return false;
   if (st[3] != 1) return false;
   if (st[2] <= 0 || st[2] % 8 != 0) return false;
   if (st[1] < 0 || st[1] % 8 != 0 || st[0] < 0 || st[0] % 8 != 0) return false;
-  (void)S;
   return true;
 }
 
@@ -818,7 +880,7 @@ int attn_tc_supported(const AttnParams& p) {
   if (p.bits == nullptr) return 0;
   if (reinterpret_cast<uintptr_t>(p.bits) % 16 != 0 || p.bits_sb % 4 != 0 || p.bits_sh % 4 != 0) return 0;
   if (!(p.scale_log2 > 0.f) || !(p.scale_log2 < 1e30f)) return 0;
-  if (!tma_friendly(p.q, p.qs, p.Sq) || !tma_friendly(p.k, p.ks, p.Sk) || !tma_friendly(p.v, p.vs, p.Sk)) return 0;
+  if (!tma_friendly(p.q, p.qs) || !tma_friendly(p.k, p.ks) || !tma_friendly(p.v, p.vs)) return 0;
   if (reinterpret_cast<uintptr_t>(p.o) % 16 != 0 || p.os[3] != 1 || p.os[2] % 8 != 0 || p.os[1] % 8 != 0 ||
       p.os[0] % 8 != 0)
     return 0;

@@ -1,5 +1,4 @@
 // extern "C" entry points declared in include/sa_b200.h: argument validation and dispatch.
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -205,10 +204,7 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   const bool tc_ok = sa::attn_tc_supported(p) != 0;
-  if (impl == SA_IMPL_TCGEN05 || (impl == SA_IMPL_AUTO && tc_ok)) {
-    static const bool use_pair = getenv("SA_TC2") != nullptr;
-    return use_pair ? sa::launch_attn_tc2(p, s) : sa::launch_attn_tc(p, s);
-  }
+  if (impl == SA_IMPL_TCGEN05 || (impl == SA_IMPL_AUTO && tc_ok)) return sa::launch_attn_tc(p, s);
 
   // generic kernel
   if (mask == nullptr || mask_strides == nullptr) return SA_ERR_INVALID_ARGUMENT;

@@ -42,16 +42,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase (try_wait may suspend the thread for a while when the phase is not complete).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: gives up after kWaitLimitNs (or as soon as another thread of the CTA
 // has given up), records that in *abort_flag (shared memory) and returns false.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 // The polling loop is out of line: a kernel has dozens of waits, and most find the phase complete.
-#ifdef SA_SETMAXNREG
-static __device__ __forceinline__
-#else
-static __device__ __noinline__
-#endif
-bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -261,27 +267,6 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   asm("add.rn.ftz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-// 2^x for a pair of fp32 values on the FMA pipe (no MUFU): round-to-nearest range reduction by
-// a magic-number add, a cubic for 2^f on [-0.5, 0.5] (relative error below 8e-5) and an integer
-// add into the exponent field.  x is clamped to >= -126, where the result is a denormal that
-// flush-to-zero arithmetic reads as 0; x must stay below 127 (callers re-do the pass long before:
-// any x above the rescale threshold forces one).
-__device__ __forceinline__ void exp2_poly_pair(float x0, float x1, float& p0, float& p1) {
-  x0 = fmaxf(x0, -126.f);
-  x1 = fmaxf(x1, -126.f);
-  const uint64_t x2 = pack_f32x2(x0, x1);
-  const uint64_t t2 = add_f32x2(x2, pack_f32x2(12582912.f, 12582912.f));
-  const uint64_t xi2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
-  const uint64_t f2 = fma_f32x2(xi2, pack_f32x2(-1.f, -1.f), x2);
-  uint64_t r2 = fma_f32x2(pack_f32x2(0.05508868f, 0.05508868f), f2, pack_f32x2(0.24260405f, 0.24260405f));
-  r2 = fma_f32x2(r2, f2, pack_f32x2(0.69327623f, 0.69327623f));
-  r2 = fma_f32x2(r2, f2, pack_f32x2(0.99992895f, 0.99992895f));
-  float r0, r1, t0, t1;
-  unpack_f32x2(r2, r0, r1);
-  unpack_f32x2(t2, t0, t1);
-  p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
-}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -289,6 +274,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Counts this warp in on a named barrier without waiting for the others.
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // ------------------------------------------------------------------ UMMA descriptors

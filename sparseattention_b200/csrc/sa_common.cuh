@@ -71,7 +71,5 @@ cudaError_t launch_attn_simt(const AttnParams& p, cudaStream_t stream);
 int attn_tc_supported(const AttnParams& p);
 // Launches the tcgen05 kernel; SA_ERR_* (negative) or 0.
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream);
-int attn_tc2_supported(const AttnParams& p);
-int launch_attn_tc2(const AttnParams& p, cudaStream_t stream);
 
 }  // namespace sa
