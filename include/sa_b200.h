@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define SA_ABI_VERSION 3
+#define SA_ABI_VERSION 4
 
 /* status codes */
 #define SA_OK                     0
@@ -167,6 +167,50 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int32_t* part_ids, const int64_t* part_ids_strides,
                 const int32_t* part_lens, const int64_t* part_lens_strides,
                 float scale_log2, int impl, float* lse, void* workspace, size_t workspace_bytes,
+                int32_t* dev_status, void* stream);
+
+/* No counterpart in the reference (its README lists a backward pass as future work, README.md:61-65).
+ * kv-major lists from the query-major lists of sa_classify_mask: for every (plane, kv block) the
+ * ascending query blocks that list it as full / as partial, tails -1.  Inputs: int32 [planes, nq, nk]
+ * ids and [planes, nq] lengths, contiguous.  Outputs: [planes, nk, nq] ids and [planes, nk] lengths. */
+int sa_transpose_lists(const int32_t* full_ids, const int32_t* full_lens,
+                       const int32_t* part_ids, const int32_t* part_lens,
+                       int planes, int nq, int nk,
+                       int32_t* t_full_ids, int32_t* t_full_lens,
+                       int32_t* t_part_ids, int32_t* t_part_lens, void* stream);
+
+/* Bytes of scratch sa_attn_bwd needs (one float per query row). */
+size_t sa_attn_bwd_workspace_bytes(int B, int H, int Sq);
+
+/* No counterpart in the reference.  Gradients of sa_attn_fwd with respect to q, k and v over the same
+ * lists: P is recomputed from lse (the forward's optional output; a row whose lse is -inf has no
+ * gradient), dV = P^T dO, dS = P * (dO V^T - D), dQ = scale dS K, dK = scale dS^T Q, with
+ * D = rowsum(dO * O) - d_lse.  CUDA-core kernels, fp32 math, any of the three dtypes, D in
+ * {16, 32, 64, 128}, block sizes that are multiples of 32; no atomics (the result does not depend on
+ * scheduling).
+ * o, d_o: the forward's output and its incoming gradient, [B,H,Sq,D] with element strides; lse: float32
+ *   [B,H,Sq] contiguous from the forward; d_lse: optional incoming gradient of lse, same layout, or NULL.
+ * dq, dk, dv: outputs with element strides, dtype of q.
+ * full_* / part_*: the query-major lists given to the forward; t_*: the kv-major lists of
+ *   sa_transpose_lists, with element strides ([B,H,nk,nq] / [B,H,nk]; 0 strides for broadcast planes).
+ * workspace: sa_attn_bwd_workspace_bytes() bytes, 4-byte aligned. */
+int sa_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                const float* lse, const float* d_lse,
+                void* dq, void* dk, void* dv,
+                const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                const int64_t* o_strides, const int64_t* do_strides,
+                const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides,
+                int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
+                const uint8_t* mask, const int64_t* mask_strides,
+                const int32_t* full_ids, const int64_t* full_ids_strides,
+                const int32_t* full_lens, const int64_t* full_lens_strides,
+                const int32_t* part_ids, const int64_t* part_ids_strides,
+                const int32_t* part_lens, const int64_t* part_lens_strides,
+                const int32_t* t_full_ids, const int64_t* t_full_ids_strides,
+                const int32_t* t_full_lens, const int64_t* t_full_lens_strides,
+                const int32_t* t_part_ids, const int64_t* t_part_ids_strides,
+                const int32_t* t_part_lens, const int64_t* t_part_lens_strides,
+                float scale_log2, void* workspace, size_t workspace_bytes,
                 int32_t* dev_status, void* stream);
 
 #ifdef __cplusplus

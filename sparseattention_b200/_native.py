@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes
 import math
 import os
-from typing import List, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -17,7 +17,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("SPARSEATTN_B200_LIB") or os.path.join(_PKG_DIR, "libsparseattn_b200.so")
 
 # mirrors of the header's constants
-SA_ABI_VERSION = 3
+SA_ABI_VERSION = 4
 SA_OK = 0
 SA_DTYPE_F32, SA_DTYPE_F16, SA_DTYPE_BF16 = 0, 1, 2
 SA_IMPL_AUTO, SA_IMPL_SIMT, SA_IMPL_TCGEN05 = 0, 1, 2
@@ -45,6 +45,15 @@ SYMBOLS = {
                          _p, _p, _p, _p, _p, _p, _p, _p,
                          _f, _i, _p, _p, _sz, _p, _p]),
     "sa_attn_workspace_bytes": (_sz, []),
+    "sa_transpose_lists": (_i, [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p]),
+    "sa_attn_bwd_workspace_bytes": (_sz, [_i, _i, _i]),
+    "sa_attn_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p,
+                         _p, _p, _p, _p, _p, _p, _p, _p,
+                         _i, _i, _i, _i, _i, _i, _i, _i,
+                         _p, _p,
+                         _p, _p, _p, _p, _p, _p, _p, _p,
+                         _p, _p, _p, _p, _p, _p, _p, _p,
+                         _f, _p, _sz, _p, _p]),
 }
 
 _lib = None
@@ -287,6 +296,107 @@ def _(q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, bl
       with_lse):
     B, H, Sq, _ = q.shape
     return q.new_empty(q.shape), q.new_empty((B, H, Sq) if with_lse else (0,), dtype=torch.float32)
+
+
+# ------------------------------------------------------------------------------- backward of stage 2
+
+def transpose_lists(full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor):
+    """kv-major lists from query-major ones: ``[P0,P1,nq,nk]`` ids / ``[P0,P1,nq]`` lengths (contiguous int32,
+    distinct planes) -> ``[P0,P1,nk,nq]`` ids (ascending query blocks, tails -1) and ``[P0,P1,nk]`` lengths,
+    for the full and for the partial lists."""
+    _require_cuda(full_ids, full_lens, part_ids, part_lens)
+    lib = load_library()
+    P0, P1, nq, nk = full_ids.shape
+    dev = full_ids.device
+    with torch.cuda.device(dev):
+        ids = lambda: torch.empty((P0, P1, nk, nq), dtype=torch.int32, device=dev)
+        lens = lambda: torch.empty((P0, P1, nk), dtype=torch.int32, device=dev)
+        tf_ids, tp_ids, tf_lens, tp_lens = ids(), ids(), lens(), lens()
+        rc = lib.sa_transpose_lists(full_ids.data_ptr(), full_lens.data_ptr(), part_ids.data_ptr(), part_lens.data_ptr(),
+                                    P0 * P1, nq, nk, tf_ids.data_ptr(), tf_lens.data_ptr(), tp_ids.data_ptr(),
+                                    tp_lens.data_ptr(), _stream_ptr(dev))
+    _check(rc, "sa_transpose_lists")
+    return tf_ids, tf_lens, tp_ids, tp_lens
+
+
+@torch.library.custom_op("sparseattention::attn_bwd", mutates_args=())
+def attn_bwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
+                lse: torch.Tensor, d_lse: Optional[torch.Tensor], mask: torch.Tensor,
+                full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
+                t_full_ids: torch.Tensor, t_full_lens: torch.Tensor, t_part_ids: torch.Tensor, t_part_lens: torch.Tensor,
+                block_q: int, block_k: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of :func:`attn_fwd_op` with respect to q, k, v (``sa_attn_bwd``): ``o`` and ``lse`` are the
+    forward's outputs, ``d_o`` / ``d_lse`` their incoming gradients, the lists the ones the forward walked and
+    their kv-major transposes (all may be expanded views)."""
+    _require_cuda(q, k, v, o, d_o, lse, mask)
+    lib = load_library()
+    B, H, Sq, D = q.shape
+    Sk = k.shape[-2]
+    dev = q.device
+    scale_log2 = D ** -0.5 / math.log(2)
+    with torch.cuda.device(dev):
+        lse = lse.contiguous()
+        gl = None if d_lse is None else d_lse.to(torch.float32).contiguous()
+        dq = torch.empty((B, H, Sq, D), dtype=q.dtype, device=dev)
+        dk = torch.empty((B, H, Sk, D), dtype=q.dtype, device=dev)
+        dv = torch.empty((B, H, Sk, D), dtype=q.dtype, device=dev)
+        ws_bytes = int(lib.sa_attn_bwd_workspace_bytes(B, H, Sq))
+        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
+        rc = lib.sa_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(),
+                             lse.data_ptr(), None if gl is None else gl.data_ptr(),
+                             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                             _strides(q), _strides(k), _strides(v), _strides(o), _strides(d_o),
+                             _strides(dq), _strides(dk), _strides(dv),
+                             _DTYPES[q.dtype], B, H, Sq, Sk, D, block_q, block_k,
+                             mask.data_ptr(), _strides(mask),
+                             full_ids.data_ptr(), _strides(full_ids), full_lens.data_ptr(), _strides(full_lens),
+                             part_ids.data_ptr(), _strides(part_ids), part_lens.data_ptr(), _strides(part_lens),
+                             t_full_ids.data_ptr(), _strides(t_full_ids), t_full_lens.data_ptr(), _strides(t_full_lens),
+                             t_part_ids.data_ptr(), _strides(t_part_ids), t_part_lens.data_ptr(), _strides(t_part_lens),
+                             scale_log2, ws.data_ptr(), ws_bytes, None, _stream_ptr(dev))
+    _check(rc, "sa_attn_bwd")
+    return dq, dk, dv
+
+
+@attn_bwd_op.register_fake
+def _(q, k, v, o, d_o, lse, d_lse, mask, full_ids, full_lens, part_ids, part_lens, t_full_ids, t_full_lens,
+      t_part_ids, t_part_lens, block_q, block_k):
+    return q.new_empty(q.shape), k.new_empty(k.shape), v.new_empty(v.shape)
+
+
+def _distinct_planes(t: torch.Tensor) -> torch.Tensor:
+    bu = 1 if (t.shape[0] == 1 or t.stride(0) == 0) else t.shape[0]
+    hu = 1 if (t.shape[1] == 1 or t.stride(1) == 0) else t.shape[1]
+    return t[:bu, :hu]
+
+
+def _attn_setup_context(ctx, inputs, output):
+    q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, block_k, impl, check_status, with_lse = inputs
+    o, lse = output
+    if not with_lse:
+        raise RuntimeError("the attention op was called without its log-sum-exp output: no backward is possible "
+                           "(sparse_attention asks for it whenever an input requires grad)")
+    ctx.save_for_backward(q, k, v, o, lse, mask, full_ids, full_lens, part_ids, part_lens)
+    ctx.blocks = (block_q, block_k)
+
+
+def _attn_backward(ctx, grad_o, grad_lse):
+    q, k, v, o, lse, mask, full_ids, full_lens, part_ids, part_lens = ctx.saved_tensors
+    block_q, block_k = ctx.blocks
+    B, H = q.shape[0], q.shape[1]
+    # kv-major lists, built over the distinct planes of the (possibly expanded) lists
+    planes = [_distinct_planes(t).contiguous() for t in (full_ids, full_lens, part_ids, part_lens)]
+    if len({tuple(t.shape[:2]) for t in planes}) != 1:
+        planes = [t.expand(B, H, *t.shape[2:]).contiguous() for t in (full_ids, full_lens, part_ids, part_lens)]
+    t_lists = transpose_lists(*planes)
+    ex = lambda t: t.expand(*((B, H) + tuple(t.shape[2:])))
+    dq, dk, dv = attn_bwd_op(q, k, v, o, grad_o.contiguous(), lse, grad_lse, mask, full_ids, full_lens, part_ids,
+                             part_lens, ex(t_lists[0]), ex(t_lists[1]), ex(t_lists[2]), ex(t_lists[3]),
+                             block_q, block_k)
+    return dq, dk, dv, None, None, None, None, None, None, None, None, None, None, None
+
+
+attn_fwd_op.register_autograd(_attn_backward, setup_context=_attn_setup_context)
 
 
 def uses_tcgen05(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, block_q: int, block_k: int,

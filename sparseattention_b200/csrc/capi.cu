@@ -213,4 +213,82 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   return sa::launch_attn_simt(p, s) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 
+int sa_transpose_lists(const int32_t* full_ids, const int32_t* full_lens,
+                       const int32_t* part_ids, const int32_t* part_lens,
+                       int planes, int nq, int nk,
+                       int32_t* t_full_ids, int32_t* t_full_lens,
+                       int32_t* t_part_ids, int32_t* t_part_lens, void* stream) {
+  if (full_ids == nullptr || full_lens == nullptr || part_ids == nullptr || part_lens == nullptr ||
+      t_full_ids == nullptr || t_full_lens == nullptr || t_part_ids == nullptr || t_part_lens == nullptr)
+    return SA_ERR_INVALID_ARGUMENT;
+  if (!positive(planes) || !positive(nq) || !positive(nk)) return SA_ERR_INVALID_ARGUMENT;
+  if (static_cast<long long>(planes) * nk > 0x7fffffffLL) return SA_ERR_UNSUPPORTED;
+  return sa::launch_transpose_lists(full_ids, full_lens, part_ids, part_lens, planes, nq, nk, t_full_ids, t_full_lens,
+                                    t_part_ids, t_part_lens, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? SA_OK : SA_ERR_CUDA;
+}
+
+size_t sa_attn_bwd_workspace_bytes(int B, int H, int Sq) {
+  if (!positive(B) || !positive(H) || !positive(Sq)) return 0;
+  return static_cast<size_t>(B) * H * Sq * sizeof(float);
+}
+
+int sa_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                const float* lse, const float* d_lse,
+                void* dq, void* dk, void* dv,
+                const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                const int64_t* o_strides, const int64_t* do_strides,
+                const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides,
+                int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
+                const uint8_t* mask, const int64_t* mask_strides,
+                const int32_t* full_ids, const int64_t* full_ids_strides,
+                const int32_t* full_lens, const int64_t* full_lens_strides,
+                const int32_t* part_ids, const int64_t* part_ids_strides,
+                const int32_t* part_lens, const int64_t* part_lens_strides,
+                const int32_t* t_full_ids, const int64_t* t_full_ids_strides,
+                const int32_t* t_full_lens, const int64_t* t_full_lens_strides,
+                const int32_t* t_part_ids, const int64_t* t_part_ids_strides,
+                const int32_t* t_part_lens, const int64_t* t_part_lens_strides,
+                float scale_log2, void* workspace, size_t workspace_bytes,
+                int32_t* dev_status, void* stream) {
+  sa::AttnBwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  if (o == nullptr || d_o == nullptr || lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr ||
+      o_strides == nullptr || do_strides == nullptr || dq_strides == nullptr || dk_strides == nullptr ||
+      dv_strides == nullptr || mask == nullptr || mask_strides == nullptr)
+    return SA_ERR_INVALID_ARGUMENT;
+  int rc = fill_attn_params(p.fwd, q, k, v, const_cast<void*>(o), q_strides, k_strides, v_strides, o_strides, dtype,
+                            B, H, Sq, Sk, D, BLOCK_Q, BLOCK_K);
+  if (rc != SA_OK) return rc;
+  if (full_ids == nullptr || full_lens == nullptr || part_ids == nullptr || part_lens == nullptr ||
+      full_ids_strides == nullptr || full_lens_strides == nullptr || part_ids_strides == nullptr ||
+      part_lens_strides == nullptr || t_full_ids == nullptr || t_full_lens == nullptr || t_part_ids == nullptr ||
+      t_part_lens == nullptr || t_full_ids_strides == nullptr || t_full_lens_strides == nullptr ||
+      t_part_ids_strides == nullptr || t_part_lens_strides == nullptr)
+    return SA_ERR_INVALID_ARGUMENT;
+  if (BLOCK_Q % 32 != 0 || BLOCK_K % 32 != 0) return SA_ERR_UNSUPPORTED;
+  if (D != 16 && D != 32 && D != 64 && D != 128) return SA_ERR_UNSUPPORTED;
+  if (workspace == nullptr || workspace_bytes < sa_attn_bwd_workspace_bytes(B, H, Sq) ||
+      reinterpret_cast<uintptr_t>(workspace) % 4 != 0)
+    return SA_ERR_WORKSPACE;
+  p.fwd.mask = mask; copy_n(p.fwd.ms, mask_strides, 4);
+  p.fwd.full_ids = full_ids; copy_n(p.fwd.fis, full_ids_strides, 4);
+  p.fwd.full_lens = full_lens; copy_n(p.fwd.fls, full_lens_strides, 3);
+  p.fwd.part_ids = part_ids; copy_n(p.fwd.pis, part_ids_strides, 4);
+  p.fwd.part_lens = part_lens; copy_n(p.fwd.pls, part_lens_strides, 3);
+  p.fwd.scale_log2 = scale_log2;
+  p.fwd.lse = const_cast<float*>(lse);
+  p.fwd.dev_status = dev_status;
+  p.d_o = d_o; copy_n(p.dos, do_strides, 4);
+  p.d_lse = d_lse;
+  p.dq = dq; p.dk = dk; p.dv = dv;
+  copy_n(p.dqs, dq_strides, 4); copy_n(p.dks, dk_strides, 4); copy_n(p.dvs, dv_strides, 4);
+  p.dsum = static_cast<float*>(workspace);
+  p.t_full_ids = t_full_ids; copy_n(p.tfis, t_full_ids_strides, 4);
+  p.t_full_lens = t_full_lens; copy_n(p.tfls, t_full_lens_strides, 3);
+  p.t_part_ids = t_part_ids; copy_n(p.tpis, t_part_ids_strides, 4);
+  p.t_part_lens = t_part_lens; copy_n(p.tpls, t_part_lens_strides, 3);
+  return sa::launch_attn_bwd_simt(p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
+}
+
 }  // extern "C"

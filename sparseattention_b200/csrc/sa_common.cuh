@@ -67,6 +67,26 @@ struct AttnParams {
 
 cudaError_t launch_attn_simt(const AttnParams& p, cudaStream_t stream);
 
+// ---------------------------------------------------------------- backward of stage 2
+struct AttnBwdParams {
+  AttnParams fwd;                                // q, k, v, o (read), lse (read), mask, query-major lists, sizes, scale
+  const void* d_o; int64_t dos[4];               // incoming gradient of O
+  const float* d_lse;                            // optional incoming gradient of lse, [B,H,Sq] contiguous
+  void* dq; void* dk; void* dv;
+  int64_t dqs[4], dks[4], dvs[4];
+  float* dsum;                                   // scratch [B,H,Sq]: per query row, sum_d dO*O (- d_lse)
+  const int32_t* t_full_ids; int64_t tfis[4];    // kv-major lists: [B,H,nk,nq] / [B,H,nk] with element strides
+  const int32_t* t_full_lens; int64_t tfls[3];
+  const int32_t* t_part_ids; int64_t tpis[4];
+  const int32_t* t_part_lens; int64_t tpls[3];
+};
+
+cudaError_t launch_transpose_lists(const int32_t* full_ids, const int32_t* full_lens, const int32_t* part_ids,
+                                   const int32_t* part_lens, int planes, int nq, int nk, int32_t* t_full_ids,
+                                   int32_t* t_full_lens, int32_t* t_part_ids, int32_t* t_part_lens,
+                                   cudaStream_t stream);
+cudaError_t launch_attn_bwd_simt(const AttnBwdParams& p, cudaStream_t stream);
+
 // Returns 1 when the tcgen05 kernel can take this call.
 int attn_tc_supported(const AttnParams& p);
 // Launches the tcgen05 kernel; SA_ERR_* (negative) or 0.

@@ -105,6 +105,12 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     exp of each row's scaled scores over its attended keys (-inf for a row with none) -- what a backward
     pass or a merge of partial attentions needs; the reference does not produce it.
 
+    Gradients: the call is differentiable with respect to q, k and v (``out.backward(...)``; also through
+    ``lse``).  The backward pass -- which the reference does not have -- recomputes P from the forward's
+    log-sum-exp and walks the same lists (CUDA-core kernels, fp32 math).  With caller-supplied lists for
+    BLOCK_Q = 32 / 64 the forward then runs the generic kernel on exactly those lists, so that forward and
+    backward see the same tiles.
+
     ``cache=True`` (with no ``mask_metadata``) keeps the lists and the packed plane of this mask and
     reuses them on every later call that passes the same mask memory, unmodified, with the same block
     sizes (see :func:`cached_mask_metadata`): stage 1 then runs once per mask, not once per layer.
@@ -122,6 +128,8 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     q, k, v = _native._tma_ready(q), _native._tma_ready(k), _native._tma_ready(v)
     impl_id = _native.IMPLS[impl]
     md = mask_metadata
+    # a backward pass needs the log-sum-exp of the forward
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
     if md is None and int(BLOCK_Q) in (32, 64) and impl_id != _native.SA_IMPL_SIMT and \
             _native.uses_tcgen05(q, k, v, 128, int(BLOCK_K), True):
         # The tensor-core kernel works on 128 query rows at a time.  With no lists from the caller
@@ -129,7 +137,7 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
         # BLOCK_Q-row blocks would be, and the bit plane masks the elements, so the result is the
         # one the finer lists would give.
         BLOCK_Q = 128
-    if md is not None and int(BLOCK_Q) in (32, 64) and impl_id != _native.SA_IMPL_SIMT and \
+    if md is not None and int(BLOCK_Q) in (32, 64) and impl_id != _native.SA_IMPL_SIMT and not needs_grad and \
             _native.uses_tcgen05(q, k, v, 128, int(BLOCK_K), True):
         merged = _merged_to_128(md, mask, int(BLOCK_Q), int(BLOCK_K))
         if merged is not None:
@@ -152,5 +160,5 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
         q, k, v, mask, bits,
         lists(md.unmasked_kv_ids, 4), lists(md.unmasked_lens, 3),
         lists(md.masked_kv_ids, 4), lists(md.masked_lens, 3),
-        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status), bool(return_lse))
+        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status), bool(return_lse or needs_grad))
     return (out, lse) if return_lse else out
