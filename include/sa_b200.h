@@ -213,6 +213,13 @@ int sa_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
                 float scale_log2, void* workspace, size_t workspace_bytes,
                 int32_t* dev_status, void* stream);
 
+/* No counterpart in the reference.  Self-test of the bounded device-side wait that every mbarrier wait of
+ * the attention kernel goes through: launches one small CTA that waits on a barrier nothing will ever
+ * arrive on, with the given limit (nanoseconds, at most 100 ms).  The wait must run out, the kernel must
+ * return by itself and *dev_status must read SA_DEV_WAIT_EXPIRED; *waited_ns (optional, device memory)
+ * receives how long the wait lasted. */
+int sa_selftest_bounded_wait(uint64_t limit_ns, int32_t* dev_status, uint64_t* waited_ns, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

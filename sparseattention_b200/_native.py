@@ -45,6 +45,7 @@ SYMBOLS = {
                          _p, _p, _p, _p, _p, _p, _p, _p,
                          _f, _i, _p, _p, _sz, _p, _p]),
     "sa_attn_workspace_bytes": (_sz, []),
+    "sa_selftest_bounded_wait": (_i, [ctypes.c_uint64, _p, _p, _p]),
     "sa_transpose_lists": (_i, [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p]),
     "sa_attn_bwd_workspace_bytes": (_sz, [_i, _i, _i]),
     "sa_attn_bwd": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p,

@@ -291,4 +291,12 @@ int sa_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   return sa::launch_attn_bwd_simt(p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 
+int sa_selftest_bounded_wait(uint64_t limit_ns, int32_t* dev_status, uint64_t* waited_ns, void* stream) {
+  if (dev_status == nullptr) return SA_ERR_INVALID_ARGUMENT;
+  if (limit_ns == 0 || limit_ns > 100ull * 1000ull * 1000ull) return SA_ERR_INVALID_ARGUMENT;   // at most 100 ms
+  return sa::launch_bounded_wait_probe(limit_ns, dev_status, reinterpret_cast<unsigned long long*>(waited_ns),
+                                       static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? SA_OK : SA_ERR_CUDA;
+}
+
 }  // extern "C"

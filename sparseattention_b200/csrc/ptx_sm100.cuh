@@ -57,13 +57,14 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // has given up), records that in *abort_flag (shared memory) and returns false.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 // The polling loop is out of line: a kernel has dozens of waits, and most find the phase complete.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                   uint64_t limit_ns = kWaitLimitNs) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xffu) == 0u) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }

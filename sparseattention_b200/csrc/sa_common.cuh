@@ -92,4 +92,9 @@ int attn_tc_supported(const AttnParams& p);
 // Launches the tcgen05 kernel; SA_ERR_* (negative) or 0.
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream);
 
+
+// One CTA that waits (bounded by limit_ns) on a barrier nothing arrives on; see selftest_sm100.cu.
+cudaError_t launch_bounded_wait_probe(unsigned long long limit_ns, int32_t* dev_status, unsigned long long* waited_ns,
+                                      cudaStream_t stream);
+
 }  // namespace sa

@@ -405,3 +405,21 @@ def test_mask_metadata_cache(native_lib, monkeypatch):
     sa.sparse_attention(q, k, v, mask, 128, 32, cache=True)
     assert len(calls) == 5
     sa.clear_mask_cache()
+
+
+def test_bounded_wait_runs_out_and_reports(native_lib):
+    """Every mbarrier wait of the tensor-core kernel is bounded.  The library's self-test waits, with a limit
+    of 1 ms, on a barrier nothing arrives on: the kernel must come back by itself, set the status word to
+    "wait expired", and have waited about as long as the limit (not the kernel's 1 s default)."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    waited = torch.zeros(1, dtype=torch.int64, device=DEV)
+    rc = native_lib.sa_selftest_bounded_wait(1_000_000, status.data_ptr(), waited.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == _native.SA_DEV_WAIT_EXPIRED
+    assert 1_000_000 <= int(waited.item()) < 50_000_000
+    # the context is still usable
+    assert int((torch.ones(4, device=DEV) * 2).sum().item()) == 8
+    assert native_lib.sa_selftest_bounded_wait(0, status.data_ptr(), None, None) == -1          # limits are bounded
+    assert native_lib.sa_selftest_bounded_wait(10**12, status.data_ptr(), None, None) == -1
