@@ -615,7 +615,10 @@ def run_ours(args):
                                     "frac_of_nominal": cls_gbs / NOMINAL["hbm_gbs"],
                                     "achieved_with_packed_plane": cls_gbs_with_plane,
                                     "frac_with_packed_plane": cls_gbs_with_plane / peaks["hbm_gbs"],
-                                    "traffic": None, "kernel": "classify_kernel",
+                                    "traffic": 279.6e6 * B / 16.0,
+                                    "traffic_unit": "bytes per launch (ncu capture at 16 mask planes: 268.6 MB read + "
+                                                    "11.0 MB written, scaled by planes)",
+                                    "kernel": "classify_kernel",
                                     "note": "algorithmic bytes (mask read once + lists; the 12.5 % of packed-plane writes "
                                             "are counted only in the *_with_packed_plane figures) / duration of the whole "
                                             "stage-1 call incl. its allocations"},
