@@ -331,22 +331,20 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
   // Ordinal `ord` of the sequence lives in ring slot ord % kTileRing.
   // A wait that fails (it ran out, or another thread's did) ends the role's loop; a warp takes that
   // decision as a whole, so that no lane is left alone in a warp-wide tensor-memory instruction.
-  auto next_tile_thread = [&](int ord) -> int {     // a role run by a single thread
+  // Whole warps wait, also where one lane acts on the result: a lone lane polling a barrier (the other
+  // lanes parked at the reconvergence point) notices its completion several times later than a full warp.
+  auto next_tile_warp = [&](int ord) -> int {
     const int slot = ord % kTileRing;
-    if (!ptx::mbar_wait(bar(BAR_TILE_FULL + slot), (ord / kTileRing) & 1, abort_flag)) return n_tiles;
+    if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_TILE_FULL + slot), (ord / kTileRing) & 1, abort_flag))) return n_tiles;
     const int t = tile_ring[slot];
-    ptx::mbar_arrive(bar(BAR_TILE_EMPTY + slot));
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(bar(BAR_TILE_EMPTY + slot));
     return t;
-  };
-  auto next_tile_warp = [&](int ord) -> int {       // a whole warp: lane 0 waits, reads and hands the slot back
-    int t = n_tiles;
-    if (lane == 0) t = next_tile_thread(ord);
-    return __shfl_sync(0xffffffffu, t, 0);
   };
   if (warp < 2) {
     // ------------------------------------------------------------------ producers
     // Warp 0 gathers Q, the K tiles and the bit-mask tiles, warp 1 the V tiles.  The whole warp
-    // runs the loop: lane 0 waits for a free stage and arms its barrier, lanes 0-7 each issue one
+    // runs the loop and waits for a free stage: lane 0 arms its barrier, lanes 0-7 each issue one
     // TMA box, lanes 0-3 fetch the list entries of a step.
     const bool is_k = warp == 0;
     const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
@@ -389,11 +387,12 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       if (total != 0) {
       if (is_k) {                                   // Q tile of this query block, double-buffered
         const int qs = tq & 1;
+        if (tq >= 2) {
+          ok = ptx::mbar_wait(bar(BAR_Q_EMPTY + qs), ((tq >> 1) - 1) & 1, abort_flag);
+          if (ok && kStageO) ok = ptx::mbar_wait(bar(BAR_Q_STORED + qs), ((tq >> 1) - 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+        }
         if (lane == 0) {
-          if (tq >= 2) {
-            ok = ptx::mbar_wait(bar(BAR_Q_EMPTY + qs), ((tq >> 1) - 1) & 1, abort_flag);
-            if (ok && kStageO) ok = ptx::mbar_wait(bar(BAR_Q_STORED + qs), ((tq >> 1) - 1) & 1, abort_flag);
-          }
           if (ok) {
             const int qb = p.qs[0] ? b : 0, qh = p.qs[1] ? h : 0;
             ptx::mbar_arrive_expect_tx(bar(BAR_Q_FULL + qs), L::kTileBytes);
@@ -443,13 +442,12 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
             tx_bytes += (e >= n_full && e < total) ? 512u : 0u;
           }
         }
-        if (lane == 0) {
-          if (round > 0) ok = ptx::mbar_wait(bar(bar_empty + st), (round - 1) & 1, abort_flag);
-          if (ok && with_bits && u >= kBitStages)
-            ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
-          if (ok) ptx::mbar_arrive_expect_tx(full_bar, tx_bytes);
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (round > 0) ok = ptx::mbar_wait(bar(bar_empty + st), (round - 1) & 1, abort_flag);
+        if (ok && with_bits && u >= kBitStages)
+          ok = ptx::mbar_wait(bar(BAR_BITS_EMPTY + bst), (u / kBitStages - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && lane == 0) ptx::mbar_arrive_expect_tx(full_bar, tx_bytes);
+        __syncwarp();
         int id_c = ids_ring[(j & 3) * 4 + (c_of_lane & 3)];
         if (static_cast<unsigned>(id_c) >= static_cast<unsigned>(nk)) { bad_index = bad_index || has_box; id_c = 0; }
         if (ok && has_box)
@@ -488,7 +486,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
     __syncwarp();
   } else if (warp == 2) {
     // ------------------------------------------------------------------ S issuer: S(g) = Q.K(g)^T  (line 40)
-    if (lane == 0) {
+    // The whole warp walks the loop and waits (a lone lane polling a barrier notices its completion
+    // several times later than a full warp does); lane 0 issues.
+    {
       constexpr uint32_t idesc_s = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, kTileN, 0);
       const uint64_t dq = ptx::umma_desc_sw128(sQ, 16u);
       const uint32_t dq_lo0 = static_cast<uint32_t>(dq), d_hi = static_cast<uint32_t>(dq >> 32);
@@ -496,84 +496,87 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       bool ok = true;
       int st = 0, round = 0, g = 0, tq = 0;
       for (int ord = 0; ok; ++ord) {
-        const int tile = next_tile_thread(ord);
+        const int tile = next_tile_warp(ord);
         if (tile >= n_tiles) break;
         const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
         if (ti.total == 0) continue;
         const int qs = tq & 1;
-        ok = ptx::mbar_wait(bar(BAR_Q_FULL + qs), (tq >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_Q_FULL + qs), (tq >> 1) & 1, abort_flag));
         const uint32_t dq_lo = dq_lo0 + qs * (L::kTileBytes >> 4);
         for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
           // Score buffer g & 1 is reused: the softmax of step g-2 has read it once P(g-2) is complete.
           // (The P buffer of the same parity is still being read by O += P.V(g-2); the softmax of
           // step g waits for that product itself before it writes P.)
           if (g >= 2) ok = ptx::mbar_wait(bar(BAR_P_FULL + (g & 1)), ((g - 2) >> 1) & 1, abort_flag);
-          if (!ok) break;
-          ok = ptx::mbar_wait(bar(BAR_K_FULL + st), round & 1, abort_flag);
+          if (ok) ok = ptx::mbar_wait(bar(BAR_K_FULL + st), round & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           ptx::tc_fence_after();
-          const uint32_t tS = tmem_base + 128u * (g & 1);
-          const uint32_t dk_lo = dk_lo0 + st * (L::kTileBytes >> 4);
+          if (lane == 0) {
+            const uint32_t tS = tmem_base + 128u * (g & 1);
+            const uint32_t dk_lo = dk_lo0 + st * (L::kTileBytes >> 4);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            constexpr uint32_t kPanelStep = kPanelBytes >> 4;
-            const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
-            if (kk == 0) ptx::mma_ss_lo<false>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
-            else         ptx::mma_ss_lo<true>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              constexpr uint32_t kPanelStep = kPanelBytes >> 4;
+              const uint32_t off = (kk / 4) * kPanelStep + (kk % 4) * 2u;      // (panel, 32-byte K slice) >> 4
+              if (kk == 0) ptx::mma_ss_lo<false>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+              else         ptx::mma_ss_lo<true>(tS, dq_lo + off, dk_lo + off, d_hi, idesc_s);
+            }
+            ptx::mma_commit(bar(BAR_K_EMPTY + st));
+            ptx::mma_commit(bar(BAR_S_FULL + (g & 1)));
+            if (j == ti.n_steps - 1) ptx::mma_commit(bar(BAR_Q_EMPTY + qs));   // Q tile no longer needed
           }
-          ptx::mma_commit(bar(BAR_K_EMPTY + st));
-          ptx::mma_commit(bar(BAR_S_FULL + (g & 1)));
-          if (j == ti.n_steps - 1) ptx::mma_commit(bar(BAR_Q_EMPTY + qs));   // Q tile no longer needed
+          __syncwarp();
           if (++st == kStagesK) { st = 0; ++round; }
         }
         ++tq;
       }
     }
-    __syncwarp();
   } else if (warp == 3) {
     // ------------------------------------------------------------------ P.V issuer: O += P(g).V(g)  (line 61)
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_o = ptx::umma_idesc_f16(Fmt<T>::umma, kTileM, D, 1);
       const uint64_t dv = ptx::umma_desc_sw128(sV, kPanelBytes);
       const uint32_t dv_lo0 = static_cast<uint32_t>(dv), dv_hi = static_cast<uint32_t>(dv >> 32);
       bool ok = true;
       int g = 0, tq = 0;
       for (int ord = 0; ok; ++ord) {
-        const int tile = next_tile_thread(ord);
+        const int tile = next_tile_warp(ord);
         if (tile >= n_tiles) break;
         const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
         if (ti.total == 0) continue;
         for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
           ok = ptx::mbar_wait(bar(BAR_P_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
-          if (!ok) break;
-          ok = ptx::mbar_wait(bar(BAR_V_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
-          if (!ok) break;
+          if (ok) ok = ptx::mbar_wait(bar(BAR_V_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
           // the first product of a tile overwrites O: the previous tile's epilogue must have read it
-          if (j == 0 && tq >= 1) ok = ptx::mbar_wait(bar(BAR_O_FREE), (tq - 1) & 1, abort_flag);
+          if (ok && j == 0 && tq >= 1) ok = ptx::mbar_wait(bar(BAR_O_FREE), (tq - 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           ptx::tc_fence_after();
-          const uint32_t tP = tmem_base + 384u + 64u * (g & 1);
-          const uint32_t dv_lo = dv_lo0 + (g & 1) * (L::kTileBytes >> 4);
-          if (j == 0) {
+          if (lane == 0) {
+            const uint32_t tP = tmem_base + 384u + 64u * (g & 1);
+            const uint32_t dv_lo = dv_lo0 + (g & 1) * (L::kTileBytes >> 4);
+            if (j == 0) {
 #pragma unroll
-            for (int kk = 0; kk < kTileN / 16; ++kk) {
-              if (kk == 0) ptx::mma_ts_lo<false>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
-              else         ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
-            }
-          } else {
+              for (int kk = 0; kk < kTileN / 16; ++kk) {
+                if (kk == 0) ptx::mma_ts_lo<false>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+                else         ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+              }
+            } else {
 #pragma unroll
-            for (int kk = 0; kk < kTileN / 16; ++kk) {
-              ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+              for (int kk = 0; kk < kTileN / 16; ++kk) {
+                ptx::mma_ts_lo<true>(tO, tP + kk * 8u, dv_lo + kk * 128u, dv_hi, idesc_o);
+              }
             }
+            ptx::mma_commit(bar(BAR_V_EMPTY + (g & 1)));
+            ptx::mma_commit(bar(BAR_PV_DONE + (g & 1)));
+            if (j == ti.n_steps - 1) ptx::mma_commit(bar(BAR_O_FULL));
           }
-          ptx::mma_commit(bar(BAR_V_EMPTY + (g & 1)));
-          ptx::mma_commit(bar(BAR_PV_DONE + (g & 1)));
-          if (j == ti.n_steps - 1) ptx::mma_commit(bar(BAR_O_FULL));
+          __syncwarp();
         }
         ++tq;
       }
     }
-    __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax
     // Thread = (query row, one of kSplit groups of 128 / kSplit score columns): the first four
