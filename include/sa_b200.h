@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define SA_ABI_VERSION 4
+#define SA_ABI_VERSION 5
 
 /* status codes */
 #define SA_OK                     0
@@ -168,6 +168,30 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int32_t* part_lens, const int64_t* part_lens_strides,
                 float scale_log2, int impl, float* lse, void* workspace, size_t workspace_bytes,
                 int32_t* dev_status, void* stream);
+
+/* No counterpart in the reference (a decode kernel is future work there, README.md:61-65).  The same
+ * operation as sa_attn_fwd for calls with few query blocks and long key sequences (decoding, short
+ * chunks of queries against a long cache), where one CTA per (query block, batch, head) leaves most of
+ * the GPU idle: the walk of every (query block, batch, head) over its two lists is cut into `splits`
+ * contiguous ranges that run as work items of their own on the tcgen05 kernel and leave normalised
+ * partial outputs and log-sum-exps in the workspace; a second kernel combines them
+ * (o = sum_s w_s o_s / sum_s w_s, w_s = exp(lse_s - max lse)).  splits = 1 is sa_attn_fwd on the tcgen05
+ * kernel.  Arguments as for sa_attn_fwd; the call must lie inside the tcgen05 kernel's set
+ * (sa_attn_uses_tcgen05), else SA_ERR_UNSUPPORTED.  workspace: sa_attn_splitkv_workspace_bytes(...) bytes,
+ * 128-byte aligned (SA_ERR_WORKSPACE otherwise); calls that may overlap on the GPU need one each. */
+size_t sa_attn_splitkv_workspace_bytes(int dtype, int B, int H, int Sq, int D, int splits);
+int sa_attn_fwd_splitkv(const void* q, const void* k, const void* v, void* o,
+                        const int64_t* q_strides, const int64_t* k_strides,
+                        const int64_t* v_strides, const int64_t* o_strides,
+                        int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
+                        const uint8_t* mask, const int64_t* mask_strides,
+                        const uint32_t* packed_bits, int64_t bits_stride_b, int64_t bits_stride_h,
+                        const int32_t* full_ids, const int64_t* full_ids_strides,
+                        const int32_t* full_lens, const int64_t* full_lens_strides,
+                        const int32_t* part_ids, const int64_t* part_ids_strides,
+                        const int32_t* part_lens, const int64_t* part_lens_strides,
+                        float scale_log2, int splits, float* lse, void* workspace, size_t workspace_bytes,
+                        int32_t* dev_status, void* stream);
 
 /* No counterpart in the reference (its README lists a backward pass as future work, README.md:61-65).
  * kv-major lists from the query-major lists of sa_classify_mask: for every (plane, kv block) the

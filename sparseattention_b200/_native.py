@@ -17,7 +17,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("SPARSEATTN_B200_LIB") or os.path.join(_PKG_DIR, "libsparseattn_b200.so")
 
 # mirrors of the header's constants
-SA_ABI_VERSION = 4
+SA_ABI_VERSION = 5
 SA_OK = 0
 SA_DTYPE_F32, SA_DTYPE_F16, SA_DTYPE_BF16 = 0, 1, 2
 SA_IMPL_AUTO, SA_IMPL_SIMT, SA_IMPL_TCGEN05 = 0, 1, 2
@@ -45,6 +45,12 @@ SYMBOLS = {
                          _p, _p, _p, _p, _p, _p, _p, _p,
                          _f, _i, _p, _p, _sz, _p, _p]),
     "sa_attn_workspace_bytes": (_sz, []),
+    "sa_attn_splitkv_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
+    "sa_attn_fwd_splitkv": (_i, [_p, _p, _p, _p, _p, _p, _p, _p,
+                                 _i, _i, _i, _i, _i, _i, _i, _i,
+                                 _p, _p, _p, _i64, _i64,
+                                 _p, _p, _p, _p, _p, _p, _p, _p,
+                                 _f, _i, _p, _p, _sz, _p, _p]),
     "sa_selftest_bounded_wait": (_i, [ctypes.c_uint64, _p, _p, _p]),
     "sa_transpose_lists": (_i, [_p, _p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p]),
     "sa_attn_bwd_workspace_bytes": (_sz, [_i, _i, _i]),
@@ -241,12 +247,13 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, bits: torch.Tensor,
                 full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
                 block_q: int, block_k: int, impl: int, check_status: bool,
-                with_lse: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+                with_lse: bool, splits: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
     """Block-sparse attention forward over precomputed lists.  ``mask`` [B,H,Sq,Sk] and the
     list tensors ([B,H,nq,nk] / [B,H,nq]) may be expanded views; ``bits`` is the packed plane
     [Bu,Hu,Sk/32,Sq] (or an empty tensor when absent).  Returns (O, LSE): LSE is float32 [B,H,Sq],
     the natural-log sum of exp of a row's scaled scores over its attended keys (-inf for none), or
-    an empty tensor when ``with_lse`` is False."""
+    an empty tensor when ``with_lse`` is False.  ``splits`` > 1 cuts every walk over the lists into that
+    many ranges that run side by side and are combined by a second kernel (tensor-core kernel only)."""
     _require_cuda(q, k, v, mask, full_ids, full_lens, part_ids, part_lens)
     lib = load_library()
     B, H, Sq, D = q.shape
@@ -271,18 +278,26 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
             bsb = bsh = 0
         status = torch.zeros((1,), dtype=torch.int32, device=dev) if check_status else None
         lse = torch.empty((B, H, Sq) if with_lse else (0,), dtype=torch.float32, device=dev)
-        ws_bytes = int(lib.sa_attn_workspace_bytes())
-        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)        # cleared by the call
-        rc = lib.sa_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                             _strides(q), _strides(k), _strides(v), _strides(o),
-                             _DTYPES[q.dtype], B, H, Sq, Sk, D, block_q, block_k,
-                             mask.data_ptr(), _strides(mask),
-                             bits.data_ptr() if has_bits else None, bsb, bsh,
-                             full_ids.data_ptr(), _strides(full_ids), full_lens.data_ptr(), _strides(full_lens),
-                             part_ids.data_ptr(), _strides(part_ids), part_lens.data_ptr(), _strides(part_lens),
-                             scale_log2, impl, lse.data_ptr() if with_lse else None, ws.data_ptr(), ws_bytes,
-                             status.data_ptr() if check_status else None, _stream_ptr(dev))
-    _check(rc, "sa_attn_fwd")
+        if splits > 1:
+            ws_bytes = int(lib.sa_attn_splitkv_workspace_bytes(_DTYPES[q.dtype], B, H, Sq, D, splits))
+        else:
+            ws_bytes = int(lib.sa_attn_workspace_bytes())
+        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)        # the counter in it is cleared by the call
+        head = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                _strides(q), _strides(k), _strides(v), _strides(o),
+                _DTYPES[q.dtype], B, H, Sq, Sk, D, block_q, block_k,
+                mask.data_ptr(), _strides(mask),
+                bits.data_ptr() if has_bits else None, bsb, bsh,
+                full_ids.data_ptr(), _strides(full_ids), full_lens.data_ptr(), _strides(full_lens),
+                part_ids.data_ptr(), _strides(part_ids), part_lens.data_ptr(), _strides(part_lens),
+                scale_log2)
+        tail = (lse.data_ptr() if with_lse else None, ws.data_ptr(), ws_bytes,
+                status.data_ptr() if check_status else None, _stream_ptr(dev))
+        if splits > 1:
+            rc = lib.sa_attn_fwd_splitkv(*head, splits, *tail)
+        else:
+            rc = lib.sa_attn_fwd(*head, impl, *tail)
+    _check(rc, "sa_attn_fwd_splitkv" if splits > 1 else "sa_attn_fwd")
     if check_status:
         code = int(status.item())
         if code != SA_DEV_OK:
@@ -294,7 +309,7 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
 
 @attn_fwd_op.register_fake
 def _(q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, block_k, impl, check_status,
-      with_lse):
+      with_lse, splits=1):
     B, H, Sq, _ = q.shape
     return q.new_empty(q.shape), q.new_empty((B, H, Sq) if with_lse else (0,), dtype=torch.float32)
 
@@ -372,7 +387,8 @@ def _distinct_planes(t: torch.Tensor) -> torch.Tensor:
 
 
 def _attn_setup_context(ctx, inputs, output):
-    q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, block_k, impl, check_status, with_lse = inputs
+    q, k, v, mask, bits, full_ids, full_lens, part_ids, part_lens, block_q, block_k, impl, check_status, with_lse = \
+        inputs[:14]
     o, lse = output
     if not with_lse:
         raise RuntimeError("the attention op was called without its log-sum-exp output: no backward is possible "
@@ -394,7 +410,7 @@ def _attn_backward(ctx, grad_o, grad_lse):
     dq, dk, dv = attn_bwd_op(q, k, v, o, grad_o.contiguous(), lse, grad_lse, mask, full_ids, full_lens, part_ids,
                              part_lens, ex(t_lists[0]), ex(t_lists[1]), ex(t_lists[2]), ex(t_lists[3]),
                              block_q, block_k)
-    return dq, dk, dv, None, None, None, None, None, None, None, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None, None, None, None, None, None, None, None
 
 
 attn_fwd_op.register_autograd(_attn_backward, setup_context=_attn_setup_context)

@@ -226,17 +226,23 @@ __device__ __noinline__ float second_pass_cold(uint32_t t_s, uint32_t t_p, uint3
   return sum;
 }
 
-// Work of one (query block, batch, head) tile, read from the lists.
+// Work of one tile -- a (query block, batch, head) or, when the walks are split, one of p.splits
+// contiguous ranges of its steps -- read from the lists.
 struct TileInfo {
   int b, h, qblk;
-  int n_full, n_part, total, n_steps, n_plain;
+  int b_out;                  // batch index of the output: the split's own slab of the partial results
+  int n_full, n_part, total;
+  int j0, j1, n_steps;        // steps [j0, j1) of the walk over the two lists; n_steps = j1 - j0
+  int n_plain;                // leading steps of the whole walk made of full blocks only
+  int m0;                     // first step of the range that carries mask words (may be >= j1)
 };
 
 // Out of line: every role calls it once per tile, and one copy keeps the kernel's code small.
 __device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq, int nk, int eps_shift) {
   TileInfo t;
-  const int bh = tile / nq;
-  t.qblk = tile % nq;
+  const int unit = tile / p.splits, split = tile - unit * p.splits;    // the splits of a unit are neighbours
+  const int bh = unit / nq;
+  t.qblk = unit % nq;
   t.b = bh / p.H;
   t.h = bh % p.H;
   int n_full = p.full_lens[t.b * p.fls[0] + t.h * p.fls[1] + static_cast<int64_t>(t.qblk) * p.fls[2]];  // line 107
@@ -244,8 +250,13 @@ __device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq
   t.n_full = min(max(n_full, 0), nk);
   t.n_part = min(max(n_part, 0), nk);
   t.total = t.n_full + t.n_part;
-  t.n_steps = (t.total + (1 << eps_shift) - 1) >> eps_shift;
-  t.n_plain = t.n_full >> eps_shift;   // leading steps made of full blocks only
+  const int all_steps = (t.total + (1 << eps_shift) - 1) >> eps_shift;
+  t.j0 = static_cast<int>(static_cast<int64_t>(all_steps) * split / p.splits);
+  t.j1 = static_cast<int>(static_cast<int64_t>(all_steps) * (split + 1) / p.splits);
+  t.n_steps = t.j1 - t.j0;
+  t.n_plain = t.n_full >> eps_shift;
+  t.m0 = max(t.n_plain, t.j0);
+  t.b_out = split * p.B + t.b;
   return t;
 }
 
@@ -383,8 +394,8 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
                                           : tile + static_cast<int>(gridDim.x);
       const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
       const int b = ti.b, h = ti.h, qblk = ti.qblk, n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps,
-                n_plain = ti.n_plain;
-      if (total != 0) {
+                n_plain = ti.n_plain, j0 = ti.j0, j1 = ti.j1;
+      if (n_steps != 0) {
       if (is_k) {                                   // Q tile of this query block, double-buffered
         const int qs = tq & 1;
         if (tq >= 2) {
@@ -413,7 +424,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       // The list entries of a step are copied to a four-step ring in shared memory two steps before
       // they are needed, asynchronously (one group per step): nothing waits for the lists' latency.
       auto fetch_ids = [&](int j) {
-        if (lane < eps && j < n_steps) {
+        if (lane < eps && j < j1) {
           const int e = (j << eps_shift) + lane;
           const int ee = e < total ? e : 0;         // slots past the end re-load the first listed block
           const int32_t* src = ee < n_full ? fids + ee * p.fis[3] : pids + (ee - n_full) * p.pis[3];   // line 33
@@ -422,9 +433,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         ptx::cp_async_commit();
       };
       __syncwarp();                                     // every lane has read the previous tile's last entries
-      fetch_ids(0);
-      fetch_ids(1);
-      for (int j = 0; j < n_steps && ok; ++j) {
+      fetch_ids(j0);
+      fetch_ids(j0 + 1);
+      for (int j = j0; j < j1 && ok; ++j) {
         fetch_ids(j + 2);
         ptx::cp_async_wait<2>();                        // the group of step j has landed
         __syncwarp();
@@ -433,7 +444,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         // The bit-mask tiles of the partial blocks of step j land on the K tile's barrier: once
         // S(j) is complete the softmax finds them in shared memory without a wait of its own.
         const bool with_bits = is_k && j >= n_plain;
-        const int u = gu + (j - n_plain), bst = u % kBitStages;
+        const int u = gu + (j - ti.m0), bst = u % kBitStages;
         uint32_t tx_bytes = L::kTileBytes;
         if (with_bits) {
 #pragma unroll
@@ -466,7 +477,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         }
         if (++st == n_stages) { st = 0; ++round; }
       }
-      gu += n_steps - n_plain;
+      gu += max(j1 - ti.m0, 0);
       ++tq;
       }
       ++ord;
@@ -499,7 +510,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         const int tile = next_tile_warp(ord);
         if (tile >= n_tiles) break;
         const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
-        if (ti.total == 0) continue;
+        if (ti.n_steps == 0) continue;
         const int qs = tq & 1;
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_Q_FULL + qs), (tq >> 1) & 1, abort_flag));
         const uint32_t dq_lo = dq_lo0 + qs * (L::kTileBytes >> 4);
@@ -544,7 +555,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         const int tile = next_tile_warp(ord);
         if (tile >= n_tiles) break;
         const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
-        if (ti.total == 0) continue;
+        if (ti.n_steps == 0) continue;
         for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
           ok = ptx::mbar_wait(bar(BAR_P_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
           if (ok) ok = ptx::mbar_wait(bar(BAR_V_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
@@ -611,12 +622,12 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
       const int n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps, n_plain = ti.n_plain;
       release_staged();
-      T* o_base = static_cast<T*>(p.o) + ti.b * p.os[0] + ti.h * p.os[1] +
+      T* o_base = static_cast<T*>(p.o) + ti.b_out * p.os[0] + ti.h * p.os[1] +
                   static_cast<int64_t>(ti.qblk) * kTileM * p.os[2];
       uint4* dst = reinterpret_cast<uint4*>(o_base + static_cast<int64_t>(row) * p.os[2] + kOC * quarter);
       float* lse_row = p.lse == nullptr ? nullptr
-          : p.lse + (static_cast<int64_t>(ti.b) * p.H + ti.h) * p.Sq + ti.qblk * kTileM + row;
-      if (total == 0) {                            // nothing attended: the rows are 0
+          : p.lse + (static_cast<int64_t>(ti.b_out) * p.H + ti.h) * p.Sq + ti.qblk * kTileM + row;
+      if (n_steps == 0) {                          // nothing attended (in this range): the rows are 0
 #pragma unroll
         for (int i = 0; i < kOC / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
         if (lse_row != nullptr && quarter == 0) *lse_row = -INFINITY;
@@ -624,8 +635,9 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       }
       float m = -INFINITY, l = 0.f;                // lines 103-104; l holds this group's partial sum
       bool gave_up = false;
-      for (int j = 0; j < n_steps; ++j) {
-        const int g = g0 + j;                      // steps since the kernel started: buffer and phase
+      for (int jj = 0; jj < n_steps; ++jj) {
+        const int j = ti.j0 + jj;                  // step of the walk over the lists
+        const int g = g0 + jj;                     // steps since the kernel started: buffer and phase
         {
           // S(g) must be complete, and so must O += P.V(g-2), which read the P buffer written below
           // (a barrier that has completed no phase yet passes a wait for parity 1).  Both are asked
@@ -655,7 +667,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
 #pragma unroll
         for (int c = 0; c < kCW / 32; ++c) w[c] = 0xffffffffu;
         if (masked) {
-          const int u = gu + (j - n_plain), st = u % kBitStages;
+          const int u = gu + (j - ti.m0), st = u % kBitStages;
 #pragma unroll
           for (int c = 0; c < kCW / 32; ++c) {
             const int ss = quarter * (kCW / 32) + c;           // sub-slot of the step
@@ -708,7 +720,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         if (second_pass) {
           // This step waited for P.V(g-2) and the previous one for P.V(g-3): the barrier of step g-1 is at
           // most one phase behind.
-          const bool rescale_o = j > 0 && __any_sync(0xffffffffu, alpha != 1.f);
+          const bool rescale_o = jj > 0 && __any_sync(0xffffffffu, alpha != 1.f);
           const float sum = second_pass_cold<T, kCW, kOC>(
               tS_mine, tP_mine, tO_mine, scale, m_new == -INFINITY ? 0.f : m_new, alpha, rescale_o,
               bar(BAR_PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, abort_flag, w[0], w[kCW / 32 - 1]);
@@ -770,7 +782,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         __syncwarp();
         if (lane == 0 && live) {
           ptx::tma_store_4d(&tm_o, slab, kOC * quarter, ti.qblk * kTileM + lq * 32, p.os[1] ? ti.h : 0,
-                            p.os[0] ? ti.b : 0);                                      // line 146
+                            p.os[0] ? ti.b_out : 0);                                  // line 146
           ptx::bulk_commit_group();
         }
         stored_slot = qs;
@@ -786,7 +798,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
         }
       }
       g0 += n_steps;
-      gu += n_steps - n_plain;
+      gu += max(ti.j1 - ti.m0, 0);
       ++tq;
     }
     release_staged();
@@ -864,7 +876,7 @@ int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& m
                                                       static_cast<int>(Smem<D>::dynamic_bytes));
   });
   if (attr_result[info->ordinal] != cudaSuccess) return SA_ERR_CUDA;
-  const int n_tiles = (p.Sq / kTileM) * p.B * p.H;
+  const int n_tiles = (p.Sq / kTileM) * p.B * p.H * p.splits;
   const int grid = n_tiles < info->sm_count ? n_tiles : info->sm_count;    // persistent: one CTA per SM walks the tiles
   if (p.tile_counter != nullptr && cudaMemsetAsync(p.tile_counter, 0, sizeof(int32_t), stream) != cudaSuccess)
     return SA_ERR_CUDA;
@@ -872,7 +884,59 @@ int launch_inst(const AttnParams& p, const CUtensorMap& mq, const CUtensorMap& m
   return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 
+// Split walks: O[row] = sum_s w_s O_s[row] / sum_s w_s with w_s = exp(lse_s - max_s lse_s), the partial
+// results being normalised outputs and natural-log sums of the ranges.  One warp per query row; a row no
+// range attended comes out as 0 with lse -inf.
+template <typename T>
+__global__ void __launch_bounds__(256)
+merge_splits_kernel(const T* __restrict__ part_o, const float* __restrict__ part_lse, int splits, int B, int H, int Sq,
+                    int D, T* __restrict__ o, int64_t os0, int64_t os1, int64_t os2, float* __restrict__ lse) {
+  const int64_t rows = static_cast<int64_t>(B) * H * Sq;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int sq = static_cast<int>(row % Sq);
+  const int h = static_cast<int>((row / Sq) % H);
+  const int b = static_cast<int>(row / (static_cast<int64_t>(Sq) * H));
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_lse[s * rows + row]);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float denom = 0.f;
+  const int per_lane = D / 32;                     // 2 or 4 consecutive elements
+  if (m > -INFINITY) {
+    for (int s = 0; s < splits; ++s) {
+      const float w = __expf(part_lse[s * rows + row] - m);
+      if (w == 0.f) continue;
+      denom += w;
+      const T* src = part_o + (s * rows + row) * D + lane * per_lane;
+      for (int i = 0; i < per_lane; ++i) acc[i] = fmaf(w, static_cast<float>(src[i]), acc[i]);
+    }
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  T* dst = o + b * os0 + h * os1 + static_cast<int64_t>(sq) * os2 + lane * per_lane;
+  for (int i = 0; i < per_lane; ++i) dst[i] = static_cast<T>(acc[i] * inv);
+  if (lse != nullptr && lane == 0) lse[row] = denom > 0.f ? m + __logf(denom) : -INFINITY;
+}
+
 }  // namespace
+
+cudaError_t launch_merge_splits(const void* part_o, const float* part_lse, int splits, int dtype, int B, int H, int Sq,
+                                int D, void* o, const int64_t* os, float* lse, cudaStream_t stream) {
+  const int64_t rows = static_cast<int64_t>(B) * H * Sq;
+  const int64_t blocks = (rows * 32 + 255) / 256;
+  if (blocks <= 0 || blocks > 0x7fffffffLL || os[3] != 1 || (D != 64 && D != 128)) return cudaErrorInvalidValue;
+  if (dtype == SA_DTYPE_BF16)
+    merge_splits_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(part_o), part_lse, splits, B, H, Sq, D, static_cast<__nv_bfloat16*>(o), os[0],
+        os[1], os[2], lse);
+  else if (dtype == SA_DTYPE_F16)
+    merge_splits_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const __half*>(part_o), part_lse, splits, B, H, Sq, D, static_cast<__half*>(o), os[0], os[1], os[2],
+        lse);
+  else
+    return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
 
 int attn_tc_supported(const AttnParams& p) {
   if (p.dtype != SA_DTYPE_F16 && p.dtype != SA_DTYPE_BF16) return 0;
@@ -892,11 +956,12 @@ int attn_tc_supported(const AttnParams& p) {
 
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
   if (!attn_tc_supported(p)) return SA_ERR_UNSUPPORTED;
+  if (p.splits < 1) return SA_ERR_INVALID_ARGUMENT;
   CUtensorMap mq, mk, mv, mo;
   if (!make_map(&mq, p.q, p.dtype, p.B, p.H, p.Sq, p.D, p.qs, kTileM)) return SA_ERR_CUDA;
   if (!make_map(&mk, p.k, p.dtype, p.B, p.H, p.Sk, p.D, p.ks, p.BK)) return SA_ERR_CUDA;
   if (!make_map(&mv, p.v, p.dtype, p.B, p.H, p.Sk, p.D, p.vs, p.BK)) return SA_ERR_CUDA;
-  if (!make_map(&mo, p.o, p.dtype, p.B, p.H, p.Sq, p.D, p.os, 32)) return SA_ERR_CUDA;     // one softmax warp's rows
+  if (!make_map(&mo, p.o, p.dtype, p.B * p.splits, p.H, p.Sq, p.D, p.os, 32)) return SA_ERR_CUDA;     // one softmax warp's rows
   if (p.dtype == SA_DTYPE_BF16) {
     return p.D == 128 ? launch_inst<__nv_bfloat16, 128>(p, mq, mk, mv, mo, stream)
                       : launch_inst<__nv_bfloat16, 64>(p, mq, mk, mv, mo, stream);

@@ -165,7 +165,24 @@ int sa_attn_uses_tcgen05(int dtype, int D, int BLOCK_Q, int BLOCK_K, int Sq, int
 
 size_t sa_attn_workspace_bytes(void) { return 16; }
 
-int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
+namespace {
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// workspace of a split walk: the tile counter, the partial log-sum-exps, the partial outputs
+struct SplitLayout {
+  size_t off_lse, off_o, total;
+};
+SplitLayout split_layout(int dtype, int B, int H, int Sq, int D, int splits) {
+  SplitLayout l;
+  const size_t rows = static_cast<size_t>(splits) * B * H * Sq;
+  l.off_lse = 16;
+  l.off_o = align_up(l.off_lse + rows * sizeof(float), 128);
+  l.total = l.off_o + rows * D * (dtype == SA_DTYPE_F32 ? 4 : 2);
+  return l;
+}
+
+int attn_fwd_common(const void* q, const void* k, const void* v, void* o,
                 const int64_t* q_strides, const int64_t* k_strides,
                 const int64_t* v_strides, const int64_t* o_strides,
                 int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
@@ -175,7 +192,7 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
                 const int32_t* full_lens, const int64_t* full_lens_strides,
                 const int32_t* part_ids, const int64_t* part_ids_strides,
                 const int32_t* part_lens, const int64_t* part_lens_strides,
-                float scale_log2, int impl, float* lse, void* workspace, size_t workspace_bytes,
+                float scale_log2, int impl, int splits, float* lse, void* workspace, size_t workspace_bytes,
                 int32_t* dev_status, void* stream) {
   sa::AttnParams p;
   if (o == nullptr || o_strides == nullptr) return SA_ERR_INVALID_ARGUMENT;
@@ -198,12 +215,33 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   p.lse = lse;
   p.dev_status = dev_status;
   p.tile_counter = nullptr;
+  p.splits = 1;
   if (workspace != nullptr && workspace_bytes >= sa_attn_workspace_bytes() &&
       reinterpret_cast<uintptr_t>(workspace) % 4 == 0)
     p.tile_counter = static_cast<int32_t*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   const bool tc_ok = sa::attn_tc_supported(p) != 0;
+  if (splits > 1) {
+    // The walk of every (query block, batch, head) over its lists is cut into `splits` ranges that run as
+    // tiles of their own and leave normalised partial outputs and log-sum-exps in the workspace; a second
+    // kernel combines them.  tcgen05 kernel only.
+    if (!tc_ok) return SA_ERR_UNSUPPORTED;
+    if (splits > 256 || static_cast<long long>(B) * splits > 0x7fffffLL) return SA_ERR_UNSUPPORTED;
+    const SplitLayout lay = split_layout(dtype, B, H, Sq, D, splits);
+    if (workspace == nullptr || workspace_bytes < lay.total || reinterpret_cast<uintptr_t>(workspace) % 128 != 0)
+      return SA_ERR_WORKSPACE;
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    sa::AttnParams ps = p;
+    ps.splits = splits;
+    ps.o = ws + lay.off_o;
+    ps.os[3] = 1; ps.os[2] = D; ps.os[1] = static_cast<int64_t>(Sq) * D; ps.os[0] = ps.os[1] * H;
+    ps.lse = reinterpret_cast<float*>(ws + lay.off_lse);
+    const int rc2 = sa::launch_attn_tc(ps, s);
+    if (rc2 != SA_OK) return rc2;
+    return sa::launch_merge_splits(ps.o, ps.lse, splits, dtype, B, H, Sq, D, o, p.os, lse, s) == cudaSuccess
+               ? SA_OK : SA_ERR_CUDA;
+  }
   if (impl == SA_IMPL_TCGEN05 || (impl == SA_IMPL_AUTO && tc_ok)) return sa::launch_attn_tc(p, s);
 
   // generic kernel
@@ -211,6 +249,51 @@ int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
   if (BLOCK_Q % 32 != 0 || BLOCK_K % 32 != 0) return SA_ERR_UNSUPPORTED;
   if (D != 16 && D != 32 && D != 64 && D != 128) return SA_ERR_UNSUPPORTED;
   return sa::launch_attn_simt(p, s) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
+}
+
+}  // namespace
+
+int sa_attn_fwd(const void* q, const void* k, const void* v, void* o,
+                const int64_t* q_strides, const int64_t* k_strides,
+                const int64_t* v_strides, const int64_t* o_strides,
+                int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
+                const uint8_t* mask, const int64_t* mask_strides,
+                const uint32_t* packed_bits, int64_t bits_stride_b, int64_t bits_stride_h,
+                const int32_t* full_ids, const int64_t* full_ids_strides,
+                const int32_t* full_lens, const int64_t* full_lens_strides,
+                const int32_t* part_ids, const int64_t* part_ids_strides,
+                const int32_t* part_lens, const int64_t* part_lens_strides,
+                float scale_log2, int impl, float* lse, void* workspace, size_t workspace_bytes,
+                int32_t* dev_status, void* stream) {
+  return attn_fwd_common(q, k, v, o, q_strides, k_strides, v_strides, o_strides, dtype, B, H, Sq, Sk, D, BLOCK_Q,
+                         BLOCK_K, mask, mask_strides, packed_bits, bits_stride_b, bits_stride_h, full_ids,
+                         full_ids_strides, full_lens, full_lens_strides, part_ids, part_ids_strides, part_lens,
+                         part_lens_strides, scale_log2, impl, 1, lse, workspace, workspace_bytes, dev_status, stream);
+}
+
+size_t sa_attn_splitkv_workspace_bytes(int dtype, int B, int H, int Sq, int D, int splits) {
+  if (!positive(B) || !positive(H) || !positive(Sq) || !positive(D) || !positive(splits)) return 0;
+  return split_layout(dtype, B, H, Sq, D, splits).total;
+}
+
+int sa_attn_fwd_splitkv(const void* q, const void* k, const void* v, void* o,
+                        const int64_t* q_strides, const int64_t* k_strides,
+                        const int64_t* v_strides, const int64_t* o_strides,
+                        int dtype, int B, int H, int Sq, int Sk, int D, int BLOCK_Q, int BLOCK_K,
+                        const uint8_t* mask, const int64_t* mask_strides,
+                        const uint32_t* packed_bits, int64_t bits_stride_b, int64_t bits_stride_h,
+                        const int32_t* full_ids, const int64_t* full_ids_strides,
+                        const int32_t* full_lens, const int64_t* full_lens_strides,
+                        const int32_t* part_ids, const int64_t* part_ids_strides,
+                        const int32_t* part_lens, const int64_t* part_lens_strides,
+                        float scale_log2, int splits, float* lse, void* workspace, size_t workspace_bytes,
+                        int32_t* dev_status, void* stream) {
+  if (splits < 1) return SA_ERR_INVALID_ARGUMENT;
+  return attn_fwd_common(q, k, v, o, q_strides, k_strides, v_strides, o_strides, dtype, B, H, Sq, Sk, D, BLOCK_Q,
+                         BLOCK_K, mask, mask_strides, packed_bits, bits_stride_b, bits_stride_h, full_ids,
+                         full_ids_strides, full_lens, full_lens_strides, part_ids, part_ids_strides, part_lens,
+                         part_lens_strides, scale_log2, SA_IMPL_TCGEN05, splits, lse, workspace, workspace_bytes,
+                         dev_status, stream);
 }
 
 int sa_transpose_lists(const int32_t* full_ids, const int32_t* full_lens,

@@ -62,6 +62,8 @@ struct AttnParams {
   float* lse;                                    // optional [B,H,Sq] contiguous: natural-log sum of exp of the scaled scores
   int32_t* dev_status;
   int32_t* tile_counter;                         // zeroed device word for the tile scheduler, or null (static order)
+  int splits;                                    // >= 1; > 1 (tcgen05 kernel only): each unit's walk over its lists is cut into
+                                                 // this many ranges, range s writing o / lse at batch index s * B + b
   int debug;
 };
 
@@ -86,6 +88,10 @@ cudaError_t launch_transpose_lists(const int32_t* full_ids, const int32_t* full_
                                    int32_t* t_full_lens, int32_t* t_part_ids, int32_t* t_part_lens,
                                    cudaStream_t stream);
 cudaError_t launch_attn_bwd_simt(const AttnBwdParams& p, cudaStream_t stream);
+
+// Combines the partial results of a split walk (see AttnParams::splits) into o (element strides os) and lse.
+cudaError_t launch_merge_splits(const void* part_o, const float* part_lse, int splits, int dtype, int B, int H, int Sq,
+                                int D, void* o, const int64_t* os, float* lse, cudaStream_t stream);
 
 // Returns 1 when the tcgen05 kernel can take this call.
 int attn_tc_supported(const AttnParams& p);

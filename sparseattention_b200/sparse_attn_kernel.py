@@ -87,9 +87,25 @@ def _merged_to_128(md: MaskMetadata, mask: torch.Tensor, block_q: int, block_k: 
                         packed_bits=bits, block_sizes=(128, block_k))
 
 
+def _pad_rows(t: torch.Tensor, n: int) -> torch.Tensor:
+    """``t`` [.., .., S, X] with ``n`` rows of zeros (False) appended along S."""
+    return torch.cat([t, t.new_zeros(t.shape[:2] + (n, t.shape[3]))], dim=2)
+
+
+_SM_COUNT = {}
+
+
+def _sm_count(device) -> int:
+    idx = torch.device(device).index
+    idx = torch.cuda.current_device() if idx is None else idx
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
 def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, BLOCK_Q, BLOCK_K,
                      mask_metadata: MaskMetadata = None, *, impl: str = "auto", check_status: bool = None,
-                     return_lse: bool = False, cache: bool = False):
+                     return_lse: bool = False, cache: bool = False, splits: int = None):
     """Block-sparse attention forward: ``softmax(q k^T / sqrt(D) + where(mask, 0, -inf)) v``
     computed only over the kv blocks listed in ``mask_metadata`` (built from the mask when
     not given), exactly the call of sparse_attn_kernel.py:149.
@@ -115,6 +131,14 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     reuses them on every later call that passes the same mask memory, unmodified, with the same block
     sizes (see :func:`cached_mask_metadata`): stage 1 then runs once per mask, not once per layer.
 
+    Few query rows against long key sequences (decoding, a short chunk of queries against a long cache):
+    with no ``mask_metadata``, a query length that is not a multiple of 128 is padded to one for the
+    tensor-core kernel (zero queries under an all-False mask; the padding rows are cut off again), and when
+    the (query block, batch, head) units are fewer than the GPU's SMs every unit's walk over its lists is
+    cut into ``splits`` ranges that run side by side and are combined by a second kernel -- the reference
+    has no such path.  ``splits=None`` picks the number (about one range per SM, at least 512 keys each);
+    ``splits=1`` switches the cutting off.
+
     ``check_status`` (default: the SPARSEATTN_B200_CHECK environment variable) makes the call
     read the kernel's device status word back, which synchronises; by default the call is
     asynchronous like the reference's.
@@ -130,6 +154,15 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     md = mask_metadata
     # a backward pass needs the log-sum-exp of the forward
     needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    pad_rows = (-Sq) % 128
+    if pad_rows and md is None and not needs_grad and impl_id != _native.SA_IMPL_SIMT and q.is_cuda and \
+            Sq % int(BLOCK_Q) == 0 and Sk % int(BLOCK_K) == 0 and \
+            _native.uses_tcgen05(_pad_rows(q[:1, :1], pad_rows), k, v, 128, int(BLOCK_K), True):
+        q = _pad_rows(q, pad_rows)
+        mask = _pad_rows(_native._distinct_planes(mask), pad_rows).expand(B, H, Sq + pad_rows, Sk)
+        BLOCK_Q, cache = 128, False
+    else:
+        pad_rows = 0
     if md is None and int(BLOCK_Q) in (32, 64) and impl_id != _native.SA_IMPL_SIMT and \
             _native.uses_tcgen05(q, k, v, 128, int(BLOCK_K), True):
         # The tensor-core kernel works on 128 query rows at a time.  With no lists from the caller
@@ -156,9 +189,23 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
         t = t if t.dtype == torch.int32 else t.to(torch.int32)
         return t.expand(*((B, H) + tuple(t.shape[2:]))) if t.dim() == nd else t
 
+    n_splits = 1
+    if int(BLOCK_Q) == 128 and impl_id != _native.SA_IMPL_SIMT and (splits is None or int(splits) > 1) and \
+            _native.uses_tcgen05(q, k, v, 128, int(BLOCK_K), bits.numel() > 0):
+        units = B * H * (q.shape[2] // 128)
+        if splits is None:
+            sms = _sm_count(q.device)
+            n_splits = max(1, min(-(-sms // units), Sk // 512, 64)) if units < sms else 1
+        else:
+            n_splits = int(splits)
+    elif splits is not None and int(splits) > 1:
+        raise NotImplementedError("splits > 1 needs the tensor-core kernel (fp16 / bf16, D 64 or 128, BLOCK_Q 128)")
+
     out, lse = _native.attn_fwd_op(
         q, k, v, mask, bits,
         lists(md.unmasked_kv_ids, 4), lists(md.unmasked_lens, 3),
         lists(md.masked_kv_ids, 4), lists(md.masked_lens, 3),
-        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status), bool(return_lse or needs_grad))
+        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status), bool(return_lse or needs_grad), n_splits)
+    if pad_rows:
+        out, lse = out[:, :, :Sq], (lse[:, :, :Sq] if lse.numel() else lse)
     return (out, lse) if return_lse else out
