@@ -195,7 +195,8 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
         units = B * H * (q.shape[2] // 128)
         if splits is None:
             sms = _sm_count(q.device)
-            n_splits = max(1, min(-(-sms // units), Sk // 512, 64)) if units < sms else 1
+            # one wave of work items: more ranges than that wait for a second turn on some SM
+            n_splits = max(1, min(sms // units, Sk // 512, 64))
         else:
             n_splits = int(splits)
     elif splits is not None and int(splits) > 1:
