@@ -161,9 +161,15 @@ def _classify_workspace(dev: torch.device, n_bytes: int) -> torch.Tensor:
     return ws
 
 
-@torch.library.custom_op("sparseattention::classify_mask", mutates_args=())
-def classify_mask_op(mask: torch.Tensor, block_q: int, block_k: int,
-                     with_bits: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+def _plain(*tensors: torch.Tensor) -> bool:
+    """True when the kernels may be called without going through the dispatcher: eager mode, ordinary
+    tensors.  (The dispatcher of a Python custom op costs tens of microseconds of host time per call, more
+    than the kernels of a small problem take; tracing, fake tensors and autograd do need it.)"""
+    return not torch.compiler.is_compiling() and all(type(t) is torch.Tensor for t in tensors)
+
+
+def _classify_mask_impl(mask: torch.Tensor, block_q: int, block_k: int,
+                        with_bits: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """mask: bool [Bu,Hu,Sq,Sk] holding only the distinct planes.  Returns
     (full_ids, full_lens, part_ids, part_lens, packed_bits) for those planes."""
     _require_cuda(mask)
@@ -195,6 +201,9 @@ def classify_mask_op(mask: torch.Tensor, block_q: int, block_k: int,
     return full_ids, full_lens, part_ids, part_lens, bits
 
 
+classify_mask_op = torch.library.custom_op("sparseattention::classify_mask", mutates_args=())(_classify_mask_impl)
+
+
 @classify_mask_op.register_fake
 def _(mask, block_q, block_k, with_bits):
     Bu, Hu, Sq, Sk = mask.shape
@@ -210,7 +219,9 @@ def classify(mask: torch.Tensor, block_q: int, block_k: int, with_bits: bool = T
     tensors of :func:`classify_mask_op` computed over the distinct planes only."""
     if mask.dim() != 4:
         raise ValueError("mask must be [B,H,Sq,Sk]")
-    return classify_mask_op(_canonical_mask(mask), int(block_q), int(block_k), bool(with_bits))
+    mask = _canonical_mask(mask)
+    fn = _classify_mask_impl if _plain(mask) else classify_mask_op
+    return fn(mask, int(block_q), int(block_k), bool(with_bits))
 
 
 def merge_lists(full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
@@ -243,8 +254,7 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
-@torch.library.custom_op("sparseattention::attn_fwd", mutates_args=())
-def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, bits: torch.Tensor,
+def _attn_fwd_impl(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, bits: torch.Tensor,
                 full_ids: torch.Tensor, full_lens: torch.Tensor, part_ids: torch.Tensor, part_lens: torch.Tensor,
                 block_q: int, block_k: int, impl: int, check_status: bool,
                 with_lse: bool, splits: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -305,6 +315,17 @@ def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.T
                                 SA_DEV_BAD_INDEX: "attention kernel: kv-block id out of range in a list"}.get(
                                     code, f"attention kernel: device status {code}"))
     return o, lse
+
+
+attn_fwd_op = torch.library.custom_op("sparseattention::attn_fwd", mutates_args=())(_attn_fwd_impl)
+
+
+def attn_fwd(*args, differentiable: bool):
+    """The attention forward: through the registered op when a backward pass may follow (or under tracing),
+    directly otherwise."""
+    if not differentiable and _plain(*args[:9]):
+        return _attn_fwd_impl(*args)
+    return attn_fwd_op(*args)
 
 
 @attn_fwd_op.register_fake

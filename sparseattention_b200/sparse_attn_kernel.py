@@ -194,19 +194,22 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
             _native.uses_tcgen05(q, k, v, 128, int(BLOCK_K), bits.numel() > 0):
         units = B * H * (q.shape[2] // 128)
         if splits is None:
+            # Only for a single query block per (batch, head): the rounding of a split call depends on the
+            # number of ranges, and calls on parts of a batch (shards) are to equal the call on the whole.
             sms = _sm_count(q.device)
             # one wave of work items: more ranges than that wait for a second turn on some SM
-            n_splits = max(1, min(sms // units, Sk // 512, 64))
+            n_splits = max(1, min(sms // units, Sk // 512, 64)) if q.shape[2] == 128 else 1
         else:
             n_splits = int(splits)
     elif splits is not None and int(splits) > 1:
         raise NotImplementedError("splits > 1 needs the tensor-core kernel (fp16 / bf16, D 64 or 128, BLOCK_Q 128)")
 
-    out, lse = _native.attn_fwd_op(
+    out, lse = _native.attn_fwd(
         q, k, v, mask, bits,
         lists(md.unmasked_kv_ids, 4), lists(md.unmasked_lens, 3),
         lists(md.masked_kv_ids, 4), lists(md.masked_lens, 3),
-        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status), bool(return_lse or needs_grad), n_splits)
+        int(BLOCK_Q), int(BLOCK_K), impl_id, bool(check_status), bool(return_lse or needs_grad), n_splits,
+        differentiable=needs_grad)
     if pad_rows:
         out, lse = out[:, :, :Sq], (lse[:, :, :Sq] if lse.numel() else lse)
     return (out, lse) if return_lse else out
