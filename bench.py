@@ -566,6 +566,7 @@ def run_ours(args):
 
     cls_ms = [statistics.mean(ev[s][2 * i].elapsed_time(ev[s][2 * i + 1]) for s in range(args.steps)) for i in range(n_p)]
     att_ms = [statistics.mean(ev[s][2 * i + 1].elapsed_time(ev[s][2 * i + 2]) for s in range(args.steps)) for i in range(n_p)]
+    att_all = [[ev[s][2 * i + 1].elapsed_time(ev[s][2 * i + 2]) for s in range(args.steps)] for i in range(n_p)]
 
     if args.profile or args.workload != "headline":
         if world > 1:
@@ -724,9 +725,10 @@ def run_ours(args):
                                             "calls between the attention launches of the timed steps (events around each: "
                                             "the gap before the kernel is in it); *_back_to_back: the same calls replayed "
                                             "from one CUDA graph, launch after launch"},
-            "sweep": [{"p": p, "classify_ms": c, "attn_ms": a, "attn_tflops": fl / (a * 1e-3) / 1e12,
+            "sweep": [{"p": p, "classify_ms": c, "attn_ms": a, "attn_ms_median": statistics.median(al),
+                       "attn_ms_best": min(al), "attn_tflops": fl / (a * 1e-3) / 1e12,
                        "classify_gbs": by / (c * 1e-3) / 1e9, "full_frac": fm, "partial_frac": pm}
-                      for p, c, a, fl, by, (fm, pm) in zip(ps, cls_ms, att_ms, flops_p, bytes_p, mix)],
+                      for p, c, a, al, fl, by, (fm, pm) in zip(ps, cls_ms, att_ms, att_all, flops_p, bytes_p, mix)],
             "list_granularities_p0.5": granularities,
             "e2e": {"value": flops_all / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps,
