@@ -86,7 +86,7 @@ struct Smem {
   static constexpr uint32_t off_bits = off_v + kStagesV * kTileBytes;      // [kBitStages][4 sub-slots][128 rows] u32
   static constexpr uint32_t off_bar = off_bits + kBitStages * 4 * 128 * 4;
   static constexpr uint32_t off_misc = off_bar + 8 * 48;
-  static constexpr uint32_t off_ids = off_misc + 16 + 4 * kTileRing;   // misc: TMEM base, abort flag, tile ring
+  static constexpr uint32_t off_ids = off_misc + 16 + 16 * kTileRing;  // misc: TMEM base, abort flag, tile ring (index and the two list lengths per slot)
   static constexpr uint32_t off_xch = off_ids + 2 * 4 * 4 * 4;         // ids: per producer warp [4 steps][4 entries]; xch: [2 parities + epilogue][kSplit column groups][128 rows] f32
   static constexpr uint32_t total = off_xch + 3 * kSplit * 128 * 4;
   static constexpr uint32_t dynamic_bytes = total + 1024;       // slack to align the base to 1024 B
@@ -237,16 +237,25 @@ struct TileInfo {
   int m0;                     // first step of the range that carries mask words (may be >= j1)
 };
 
+// The two list lengths of a tile's (query block, batch, head), read from global memory: by the
+// scheduling warp only, which hands them to the other roles with the tile index.
+__device__ __forceinline__ void tile_lens(const AttnParams& p, int tile, int nq, int& n_full, int& n_part) {
+  const int unit = tile / p.splits;
+  const int bh = unit / nq, qblk = unit % nq;
+  const int b = bh / p.H, h = bh % p.H;
+  n_full = p.full_lens[b * p.fls[0] + h * p.fls[1] + static_cast<int64_t>(qblk) * p.fls[2]];  // line 107
+  n_part = p.part_lens[b * p.pls[0] + h * p.pls[1] + static_cast<int64_t>(qblk) * p.pls[2]];  // line 127
+}
+
 // Out of line: every role calls it once per tile, and one copy keeps the kernel's code small.
-__device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int nq, int nk, int eps_shift) {
+__device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int n_full, int n_part, int nq, int nk,
+                                           int eps_shift) {
   TileInfo t;
   const int unit = tile / p.splits, split = tile - unit * p.splits;    // the splits of a unit are neighbours
   const int bh = unit / nq;
   t.qblk = unit % nq;
   t.b = bh / p.H;
   t.h = bh % p.H;
-  int n_full = p.full_lens[t.b * p.fls[0] + t.h * p.fls[1] + static_cast<int64_t>(t.qblk) * p.fls[2]];  // line 107
-  int n_part = p.part_lens[t.b * p.pls[0] + t.h * p.pls[1] + static_cast<int64_t>(t.qblk) * p.pls[2]];  // line 127
   t.n_full = min(max(n_full, 0), nk);
   t.n_part = min(max(n_part, 0), nk);
   t.total = t.n_full + t.n_part;
@@ -344,10 +353,12 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
   // decision as a whole, so that no lane is left alone in a warp-wide tensor-memory instruction.
   // Whole warps wait, also where one lane acts on the result: a lone lane polling a barrier (the other
   // lanes parked at the reconvergence point) notices its completion several times later than a full warp.
-  auto next_tile_warp = [&](int ord) -> int {
+  auto next_tile_warp = [&](int ord, int& n_full, int& n_part) -> int {
     const int slot = ord % kTileRing;
     if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_TILE_FULL + slot), (ord / kTileRing) & 1, abort_flag))) return n_tiles;
-    const int t = tile_ring[slot];
+    const int t = tile_ring[4 * slot];
+    n_full = tile_ring[4 * slot + 1];
+    n_part = tile_ring[4 * slot + 2];
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(bar(BAR_TILE_EMPTY + slot));
     return t;
@@ -375,16 +386,27 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
     int st = 0, round = 0, gu = 0, tq = 0;
     const uint32_t s_ids = sbase + L::off_ids + static_cast<uint32_t>(warp) * 64u;
     const volatile int* ids_ring = reinterpret_cast<const volatile int*>(smem + L::off_ids + warp * 64);
-    // lane 0 of warp 0 publishes tile `t` as ordinal `ord` of the sequence
-    auto publish = [&](int ord, int t) {
+    // lane 0 of warp 0 publishes tile `t`, with its two list lengths, as ordinal `ord` of the sequence
+    auto publish = [&](int ord, int t, int n_full, int n_part) {
       const int slot = ord % kTileRing;
       if (ord >= kTileRing) ok = ptx::mbar_wait(bar(BAR_TILE_EMPTY + slot), (ord / kTileRing - 1) & 1, abort_flag);
-      tile_ring[slot] = (ok && *abort_flag == 0) ? t : n_tiles;    // after a failed wait every role is sent home
+      tile_ring[4 * slot] = (ok && *abort_flag == 0) ? t : n_tiles;    // after a failed wait every role is sent home
+      tile_ring[4 * slot + 1] = n_full;
+      tile_ring[4 * slot + 2] = n_part;
       ptx::mbar_arrive(bar(BAR_TILE_FULL + slot));
     };
     int ord = 0;
-    int tile = blockIdx.x;
-    if (is_k) { if (lane == 0) publish(0, tile); } else { tile = next_tile_warp(0); }
+    int tile = blockIdx.x, len_f = 0, len_p = 0;
+    if (is_k) {
+      if (lane == 0) {
+        if (tile < n_tiles) tile_lens(p, tile, nq, len_f, len_p);
+        publish(0, tile, len_f, len_p);
+      }
+      len_f = __shfl_sync(0xffffffffu, len_f, 0);
+      len_p = __shfl_sync(0xffffffffu, len_p, 0);
+    } else {
+      tile = next_tile_warp(0, len_f, len_p);
+    }
     while (tile < n_tiles && ok) {
       // The next tile is drawn now and published after this one's loads are issued: the answer of
       // the atomic is not waited for until then.
@@ -392,7 +414,7 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       if (is_k && lane == 0)
         drawn = p.tile_counter != nullptr ? atomicAdd(p.tile_counter, 1) + static_cast<int>(gridDim.x)
                                           : tile + static_cast<int>(gridDim.x);
-      const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
+      const TileInfo ti = tile_info(p, tile, len_f, len_p, nq, nk, eps_shift);
       const int b = ti.b, h = ti.h, qblk = ti.qblk, n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps,
                 n_plain = ti.n_plain, j0 = ti.j0, j1 = ti.j1;
       if (n_steps != 0) {
@@ -484,12 +506,16 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       if (is_k) {
         if (lane == 0) {
           if (drawn < 0 || drawn > n_tiles) drawn = n_tiles;
-          publish(ord, drawn);
+          len_f = len_p = 0;
+          if (drawn < n_tiles) tile_lens(p, drawn, nq, len_f, len_p);   // this tile's loads are all under way by now
+          publish(ord, drawn, len_f, len_p);
         }
         tile = __shfl_sync(0xffffffffu, drawn, 0);
+        len_f = __shfl_sync(0xffffffffu, len_f, 0);
+        len_p = __shfl_sync(0xffffffffu, len_p, 0);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       } else {
-        tile = next_tile_warp(ord);
+        tile = next_tile_warp(ord, len_f, len_p);
       }
     }
     if (is_k && __any_sync(0xffffffffu, bad_index) && lane == 0 && p.dev_status != nullptr)
@@ -507,9 +533,10 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       bool ok = true;
       int st = 0, round = 0, g = 0, tq = 0;
       for (int ord = 0; ok; ++ord) {
-        const int tile = next_tile_warp(ord);
+        int len_f, len_p;
+        const int tile = next_tile_warp(ord, len_f, len_p);
         if (tile >= n_tiles) break;
-        const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
+        const TileInfo ti = tile_info(p, tile, len_f, len_p, nq, nk, eps_shift);
         if (ti.n_steps == 0) continue;
         const int qs = tq & 1;
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(bar(BAR_Q_FULL + qs), (tq >> 1) & 1, abort_flag));
@@ -552,9 +579,10 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       bool ok = true;
       int g = 0, tq = 0;
       for (int ord = 0; ok; ++ord) {
-        const int tile = next_tile_warp(ord);
+        int len_f, len_p;
+        const int tile = next_tile_warp(ord, len_f, len_p);
         if (tile >= n_tiles) break;
-        const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
+        const TileInfo ti = tile_info(p, tile, len_f, len_p, nq, nk, eps_shift);
         if (ti.n_steps == 0) continue;
         for (int j = 0; j < ti.n_steps && ok; ++j, ++g) {
           ok = ptx::mbar_wait(bar(BAR_P_FULL + (g & 1)), (g >> 1) & 1, abort_flag);
@@ -617,9 +645,10 @@ attn_fwd_tc_kernel(const __grid_constant__ AttnParams p,
       }
     };
     for (int ord = 0;; ++ord) {
-      const int tile = next_tile_warp(ord);
+      int len_f, len_p;
+      const int tile = next_tile_warp(ord, len_f, len_p);
       if (tile >= n_tiles) break;
-      const TileInfo ti = tile_info(p, tile, nq, nk, eps_shift);
+      const TileInfo ti = tile_info(p, tile, len_f, len_p, nq, nk, eps_shift);
       const int n_full = ti.n_full, total = ti.total, n_steps = ti.n_steps, n_plain = ti.n_plain;
       release_staged();
       T* o_base = static_cast<T*>(p.o) + ti.b_out * p.os[0] + ti.h * p.os[1] +
