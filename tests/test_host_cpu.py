@@ -128,3 +128,26 @@ def test_reference_module_names_resolve_to_this_library():
     assert hasattr(torch.ops.sparseattention, "classify_mask") and hasattr(torch.ops.sparseattention, "attn_fwd")
     with pytest.raises(RuntimeError):           # CUDA tensors only: no CPU implementation is registered
         mu.compute_mask_kernel(torch.ones((1, 1, 128, 128), dtype=torch.bool), 128, 32)
+
+
+def test_reference_arm_of_the_bench_prints_one_contract_line():
+    """``bench.py --impl reference`` needs no GPU: one JSON line with the contract's keys, the CPU arm's
+    own figures in ``value`` / ``cpu_baseline`` / ``e2e``, no GPU launches claimed."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "1", "--cpu-heads", "1"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e", "impl"):
+        assert key in line, key
+    assert line["impl"] == "reference" and line["value"] > 0 and line["gpu_launches"] == 0
+    assert line["e2e"]["value"] == line["value"] and line["cpu_baseline"]["value"] == line["value"]
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert line["cpu_baseline"]["kind"] in ("port", "reference") and line["cpu_baseline"]["cores"] >= 1
