@@ -157,7 +157,7 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
     pad_rows = (-Sq) % 128
     if pad_rows and md is None and not needs_grad and impl_id != _native.SA_IMPL_SIMT and q.is_cuda and \
             Sq % int(BLOCK_Q) == 0 and Sk % int(BLOCK_K) == 0 and \
-            _native.uses_tcgen05(_pad_rows(q[:1, :1], pad_rows), k, v, 128, int(BLOCK_K), True):
+            _native.uses_tcgen05(k[:, :, :128], k, v, 128, int(BLOCK_K), True):   # the padded q is fresh and dense: k stands in
         q = _pad_rows(q, pad_rows)
         mask = _pad_rows(_native._distinct_planes(mask), pad_rows).expand(B, H, Sq + pad_rows, Sk)
         BLOCK_Q, cache = 128, False
