@@ -251,21 +251,25 @@ __device__ __forceinline__ void tile_lens(const AttnParams& p, int tile, int nq,
 __device__ __noinline__ TileInfo tile_info(const AttnParams& p, int tile, int n_full, int n_part, int nq, int nk,
                                            int eps_shift) {
   TileInfo t;
-  const int unit = tile / p.splits, split = tile - unit * p.splits;    // the splits of a unit are neighbours
-  const int bh = unit / nq;
-  t.qblk = unit % nq;
-  t.b = bh / p.H;
-  t.h = bh % p.H;
+  // (unsigned 32-bit divisions, and none where the divisor is 1: every role pays for this at each tile)
+  const unsigned utile = static_cast<unsigned>(tile), usplits = static_cast<unsigned>(p.splits);
+  const unsigned unit = usplits == 1u ? utile : utile / usplits;      // the splits of a unit are neighbours
+  const unsigned split = usplits == 1u ? 0u : utile - unit * usplits;
+  const unsigned bh = unit / static_cast<unsigned>(nq);
+  t.qblk = static_cast<int>(unit - bh * static_cast<unsigned>(nq));
+  t.b = static_cast<int>(bh / static_cast<unsigned>(p.H));
+  t.h = static_cast<int>(bh - static_cast<unsigned>(t.b) * static_cast<unsigned>(p.H));
   t.n_full = min(max(n_full, 0), nk);
   t.n_part = min(max(n_part, 0), nk);
   t.total = t.n_full + t.n_part;
   const int all_steps = (t.total + (1 << eps_shift) - 1) >> eps_shift;
-  t.j0 = static_cast<int>(static_cast<int64_t>(all_steps) * split / p.splits);
-  t.j1 = static_cast<int>(static_cast<int64_t>(all_steps) * (split + 1) / p.splits);
+  // all_steps < 2^23 (two lists of Sk / 32 entries at most) and splits <= 256: the products fit 32 bits
+  t.j0 = usplits == 1u ? 0 : static_cast<int>(static_cast<unsigned>(all_steps) * split / usplits);
+  t.j1 = usplits == 1u ? all_steps : static_cast<int>(static_cast<unsigned>(all_steps) * (split + 1u) / usplits);
   t.n_steps = t.j1 - t.j0;
   t.n_plain = t.n_full >> eps_shift;
   t.m0 = max(t.n_plain, t.j0);
-  t.b_out = split * p.B + t.b;
+  t.b_out = static_cast<int>(split) * p.B + t.b;
   return t;
 }
 
