@@ -465,6 +465,50 @@ def run_decode(args):
     }))
 
 
+# ------------------------------------------------------------------------------- backward pass
+
+def run_backward(args):
+    """Kernel-only figures for forward + backward through autograd (the reference has no backward pass,
+    README.md:61-65): a slice of the headline shape, p = 0.5, against torch SDPA with the bool mask on the same GPU."""
+    import sparseattention_b200 as sa
+    import workloads
+    from sparseattention_b200 import _native
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    _native.load_library()
+    B, H, S, D, BQ, BK = (args.batch or 1), 8, 4096, 128, 128, 32
+    q, k, v = (t.requires_grad_(True) for t in workloads.make_qkv(B, H, S, D, torch.bfloat16, seed=5, device=dev))
+    mask = workloads.random_block_mask(B, S, 0.5, 0.1, seed=6, device=dev)
+    md = sa.compute_mask_kernel(mask.expand(B, H, S, S), BQ, BK)
+    g = torch.randn((B, H, S, D), device=dev, dtype=torch.bfloat16)
+    flops_fwd = workloads.computed_tile_flops(md.unmasked_lens, md.masked_lens, BQ, BK, D)
+
+    def ours():
+        out = sa.sparse_attention(q, k, v, mask, BQ, BK, mask_metadata=md)
+        out.backward(g)
+        q.grad = k.grad = v.grad = None
+
+    mask_e = mask.expand(B, H, S, S)
+
+    def sdpa():
+        out = torch.nn.functional.scaled_dot_product_attention(q, k, v, attn_mask=mask_e)
+        out.backward(g)
+        q.grad = k.grad = v.grad = None
+
+    fwd_ms = best_ms(lambda: sa.sparse_attention(q.detach(), k.detach(), v.detach(), mask, BQ, BK, mask_metadata=md), n=5, warm=2)
+    ours_ms = best_ms(ours, n=3, warm=1)
+    sdpa_ms = best_ms(sdpa, n=3, warm=1)
+    print(json.dumps({
+        "workload": f"forward + backward: B={B} H={H} S={S} D={D} bf16, 32x32-block mask, drop p=0.5, lists at ({BQ},{BK})",
+        "forward_ms": fwd_ms, "forward_plus_backward_ms": ours_ms, "backward_ms": ours_ms - fwd_ms,
+        "backward_tflops_over_listed_tiles": 2.5 * flops_fwd / ((ours_ms - fwd_ms) * 1e-3) / 1e12,
+        "torch_sdpa_bool_mask_forward_plus_backward_ms": sdpa_ms,
+        "note": "backward = kv-major list transpose + dQ and dK/dV kernels on the tensor cores (warp-level MMA, fp32 accumulation); "
+                "2.5 x the forward's FLOPs over the listed tiles",
+    }))
+
+
 # ------------------------------------------------------------------------------- GPU arm
 
 def run_ours(args):
@@ -865,7 +909,7 @@ def main():
     ap.add_argument("--results-json", default="", help="also write the attention_results record to this file")
     ap.add_argument("--profile", action="store_true",
                     help="profiling run: kernels only (no end-to-end leg, no CPU baseline, no warm-up floor)")
-    ap.add_argument("--workload", default="headline", choices=["headline", "document", "composed", "scaling", "decode"],
+    ap.add_argument("--workload", default="headline", choices=["headline", "document", "composed", "scaling", "decode", "backward"],
                     help="headline = the benchmark line; the others print kernel-only figures for that configuration "
                          "(decode: 32 query rows against 32768 keys, one GPU)")
     ap.add_argument("--batch", type=int, default=0, help="profiling: override the batch size of the workload")
@@ -877,6 +921,8 @@ def main():
         run_reference(args)
     elif args.workload == "decode":
         run_decode(args)
+    elif args.workload == "backward":
+        run_backward(args)
     else:
         run_ours(args)
     out.flush()

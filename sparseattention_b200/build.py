@@ -15,7 +15,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 INCLUDE = os.path.join(os.path.dirname(PKG_DIR), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libsparseattn_b200.so")
-SOURCES = ["classify_sm100.cu", "attn_simt.cu", "attn_bwd_simt.cu", "attn_fwd_sm100.cu", "selftest_sm100.cu", "capi.cu"]
+SOURCES = ["classify_sm100.cu", "attn_simt.cu", "attn_bwd_simt.cu", "attn_bwd_mma.cu", "attn_fwd_sm100.cu", "selftest_sm100.cu", "capi.cu"]
 HEADERS = ["sa_common.cuh", "ptx_sm100.cuh"]
 
 

@@ -371,6 +371,9 @@ int sa_attn_bwd(const void* q, const void* k, const void* v, const void* o, cons
   p.t_full_lens = t_full_lens; copy_n(p.tfls, t_full_lens_strides, 3);
   p.t_part_ids = t_part_ids; copy_n(p.tpis, t_part_ids_strides, 4);
   p.t_part_lens = t_part_lens; copy_n(p.tpls, t_part_lens_strides, 3);
+  // tensor-core kernels where the inputs allow them (fp16 / bf16, head dim 64 or 128, dense rows), else the CUDA-core ones
+  if (sa::attn_bwd_mma_supported(p))
+    return sa::launch_attn_bwd_mma(p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
   return sa::launch_attn_bwd_simt(p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? SA_OK : SA_ERR_CUDA;
 }
 

@@ -88,6 +88,9 @@ cudaError_t launch_transpose_lists(const int32_t* full_ids, const int32_t* full_
                                    int32_t* t_full_lens, int32_t* t_part_ids, int32_t* t_part_lens,
                                    cudaStream_t stream);
 cudaError_t launch_attn_bwd_simt(const AttnBwdParams& p, cudaStream_t stream);
+// Tensor-core version (fp16 / bf16, head dim 64 or 128, unit stride along the head dim, 16-byte aligned rows).
+int attn_bwd_mma_supported(const AttnBwdParams& p);
+cudaError_t launch_attn_bwd_mma(const AttnBwdParams& p, cudaStream_t stream);
 
 // Combines the partial results of a split walk (see AttnParams::splits) into o (element strides os) and lse.
 cudaError_t launch_merge_splits(const void* part_o, const float* part_lse, int splits, int dtype, int B, int H, int Sq,
