@@ -30,23 +30,26 @@ namespace {
 
 using namespace nvcuda;
 
-constexpr int kR = 32;            // rows a CTA owns
 constexpr int kC = 32;            // rows of the other side per chunk
-constexpr int kWarps = kR / 16;
-constexpr int kThreadsMma = 32 * kWarps;
 constexpr int kLdT = kC + 4;      // fp32 scratch rows (floats)
 constexpr int kLdE = kC + 8;      // P / dS rows (elements)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
-template <int D> struct BwdSmem {
+// R = rows a CTA owns (32, 64 or 128: never more than the block size of its side, so that all of them
+// walk the same lists); a warp owns 16 of them.
+template <int D, int R> struct BwdSmem {
+  static constexpr int kWarps = R / 16;
   static constexpr int kLd = D + 8;                                 // rows of the staged tiles (elements): 16 bytes of padding
-  static constexpr size_t tile = static_cast<size_t>(kR) * kLd * 2;           // bytes of one 32 x D tile
-  static constexpr size_t off_a1 = 0, off_a2 = tile, off_b1 = 2 * tile, off_b2 = 3 * tile;
-  static constexpr size_t off_t = 4 * tile;                                   // [warp][2][16][kLdT] float
+  static constexpr size_t tile_a = static_cast<size_t>(R) * kLd * 2;          // bytes of one R x D tile
+  static constexpr size_t tile_b = static_cast<size_t>(kC) * kLd * 2;         // bytes of one 32 x D tile
+  static constexpr size_t off_a1 = 0, off_a2 = tile_a;
+  static constexpr size_t off_b = 2 * tile_a;                                 // [2 buffers][2 tiles]
+  static constexpr size_t off_t = off_b + 4 * tile_b;                         // [warp][2][16][kLdT] float
   static constexpr size_t off_e = off_t + static_cast<size_t>(kWarps) * 2 * 16 * kLdT * 4;   // [warp][2][16][kLdE] T
-  static constexpr size_t off_stat = off_e + static_cast<size_t>(kWarps) * 2 * 16 * kLdE * 2;  // lse2[32], dsum[32] (own rows), then the chunk's
-  static constexpr size_t total = off_stat + 4 * 32 * 4;
+  static constexpr size_t off_mask = off_e + static_cast<size_t>(kWarps) * 2 * 16 * kLdE * 2;  // [2 buffers][R * 32] bytes
+  static constexpr size_t off_stat = off_mask + 2 * static_cast<size_t>(R) * kC;             // own lse2[R], dsum[R]; chunk's [2][2][32]
+  static constexpr size_t total = off_stat + (2 * R + 4 * kC) * 4;
 };
 
 template <typename T> __device__ __forceinline__ T from_float(float x);
@@ -56,32 +59,41 @@ template <typename T> __device__ __forceinline__ float to_float(T x);
 template <> __device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
 
-// 32 rows x D elements from global memory (unit stride along D, 16-byte aligned rows) into a padded tile
-template <typename T, int D>
-__device__ __forceinline__ void load_tile(T* dst, const T* src, int64_t row_stride, int tid) {
-  constexpr int kLd = BwdSmem<D>::kLd;
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// `rows` rows x D elements from global memory (unit stride along D, 16-byte aligned rows) into a padded
+// tile, asynchronously (cp.async, 16 bytes each)
+template <typename T, int D, int kThreads>
+__device__ __forceinline__ void load_tile_async(T* dst, const T* src, int64_t row_stride, int rows, int tid) {
+  constexpr int kLd = D + 8;
   constexpr int kVecPerRow = D / 8;                       // 16-byte vectors
-  for (int e = tid; e < kR * kVecPerRow; e += kThreadsMma) {
+  for (int e = tid; e < rows * kVecPerRow; e += kThreads) {
     const int r = e / kVecPerRow, c = e % kVecPerRow;
-    const uint4 v = *reinterpret_cast<const uint4*>(src + static_cast<int64_t>(r) * row_stride + c * 8);
-    *reinterpret_cast<uint4*>(dst + r * kLd + c * 8) = v;
+    cp_async_16(dst + r * kLd + c * 8, src + static_cast<int64_t>(r) * row_stride + c * 8);
   }
 }
 
-template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(kThreadsMma)
-attn_bwd_mma_kernel(const AttnBwdParams p) {
-  using S = BwdSmem<D>;
+template <typename T, int D, int R, int MODE>
+__global__ void __launch_bounds__(2 * R)
+attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
+  using S = BwdSmem<D, R>;
   constexpr int kLd = S::kLd;
+  constexpr int kThreads = 2 * R;
   extern __shared__ __align__(128) uint8_t smem[];
   T* sA1 = reinterpret_cast<T*>(smem + S::off_a1);
   T* sA2 = reinterpret_cast<T*>(smem + S::off_a2);
-  T* sB1 = reinterpret_cast<T*>(smem + S::off_b1);
-  T* sB2 = reinterpret_cast<T*>(smem + S::off_b2);
-  float* s_lse2 = reinterpret_cast<float*>(smem + S::off_stat);      // own rows (mode 0) / unused (mode 1)
-  float* s_dsum = s_lse2 + 32;
-  float* c_lse2 = s_lse2 + 64;                                        // the chunk's query rows (mode 1)
-  float* c_dsum = s_lse2 + 96;
+  T* sB = reinterpret_cast<T*>(smem + S::off_b);                       // buffer u & 1: tiles B1 then B2
+  uint8_t* s_mask = smem + S::off_mask;                                // buffer u & 1: the chunk's mask bytes
+  float* s_lse2 = reinterpret_cast<float*>(smem + S::off_stat);      // own rows (mode 0)
+  float* s_dsum = s_lse2 + R;
+  float* c_stat = s_lse2 + 2 * R;                                      // the chunk's query rows (mode 1): [buffer][lse2 | dsum][32]
   const AttnParams& f = p.fwd;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -89,13 +101,14 @@ attn_bwd_mma_kernel(const AttnBwdParams p) {
   T* sE = reinterpret_cast<T*>(smem + S::off_e) + warp * 2 * 16 * kLdE;
 
   const int rows_total = MODE == 0 ? f.Sq : f.Sk;
-  const int groups = rows_total / kR;
-  const int row0 = static_cast<int>(blockIdx.x % groups) * kR;        // first row this CTA owns
+  const int groups = rows_total / R;
+  const int row0 = static_cast<int>(blockIdx.x % groups) * R;         // first row this CTA owns
   const int bh = static_cast<int>(blockIdx.x / groups);
   const int b = bh / f.H, h = bh % f.H;
   const int own_blk = row0 / (MODE == 0 ? f.BQ : f.BK);
   const int n_other = MODE == 0 ? f.Sk / f.BK : f.Sq / f.BQ;          // blocks on the other side
   const int other_rows = MODE == 0 ? f.BK : f.BQ;
+  const int cpb = other_rows / kC;                                    // chunks per block of the other side
 
   const T* qbase = static_cast<const T*>(f.q) + b * f.qs[0] + h * f.qs[1];
   const T* kbase = static_cast<const T*>(f.k) + b * f.ks[0] + h * f.ks[1];
@@ -104,10 +117,72 @@ attn_bwd_mma_kernel(const AttnBwdParams p) {
   const uint8_t* mbase = f.mask + b * f.ms[0] + h * f.ms[1];
   const int64_t stat0 = (static_cast<int64_t>(b) * f.H + h) * f.Sq;
 
+  // the two lists this CTA walks: the full one first, then the partial one (the forward's order)
+  const int32_t *fids, *pids;
+  int64_t fstr, pstr;
+  int nf, np;
+  if (MODE == 0) {
+    fids = f.full_ids + b * f.fis[0] + h * f.fis[1] + static_cast<int64_t>(own_blk) * f.fis[2];
+    pids = f.part_ids + b * f.pis[0] + h * f.pis[1] + static_cast<int64_t>(own_blk) * f.pis[2];
+    fstr = f.fis[3]; pstr = f.pis[3];
+    nf = f.full_lens[b * f.fls[0] + h * f.fls[1] + static_cast<int64_t>(own_blk) * f.fls[2]];
+    np = f.part_lens[b * f.pls[0] + h * f.pls[1] + static_cast<int64_t>(own_blk) * f.pls[2]];
+  } else {
+    fids = p.t_full_ids + b * p.tfis[0] + h * p.tfis[1] + static_cast<int64_t>(own_blk) * p.tfis[2];
+    pids = p.t_part_ids + b * p.tpis[0] + h * p.tpis[1] + static_cast<int64_t>(own_blk) * p.tpis[2];
+    fstr = p.tfis[3]; pstr = p.tpis[3];
+    nf = p.t_full_lens[b * p.tfls[0] + h * p.tfls[1] + static_cast<int64_t>(own_blk) * p.tfls[2]];
+    np = p.t_part_lens[b * p.tpls[0] + h * p.tpls[1] + static_cast<int64_t>(own_blk) * p.tpls[2]];
+  }
+  nf = min(max(nf, 0), n_other);
+  np = min(max(np, 0), n_other);
+  const int total_chunks = (nf + np) * cpb;
+
+  // chunk u of the walk: first row on the other side (-1 for an id out of range), and whether the mask applies
+  auto chunk_of = [&](int u, bool& masked) -> int {
+    const int e = u / cpb, sub = (u - e * cpb) * kC;
+    masked = e >= nf;
+    const int id = masked ? pids[(e - nf) * pstr] : fids[e * fstr];
+    if (id < 0 || id >= n_other) return -1;
+    return id * other_rows + sub;
+  };
+  // requests chunk u into buffer u & 1 (every thread takes part; one cp.async group per chunk)
+  auto request = [&](int u) {
+    bool masked;
+    const int c0 = chunk_of(u, masked);
+    const int buf = u & 1;
+    if (c0 >= 0) {
+      T* b1 = sB + static_cast<size_t>(buf) * 2 * kC * kLd;
+      T* b2 = b1 + kC * kLd;
+      if (MODE == 0) {
+        load_tile_async<T, D, kThreads>(b1, kbase + static_cast<int64_t>(c0) * f.ks[2], f.ks[2], kC, tid);
+        load_tile_async<T, D, kThreads>(b2, vbase + static_cast<int64_t>(c0) * f.vs[2], f.vs[2], kC, tid);
+      } else {
+        load_tile_async<T, D, kThreads>(b1, qbase + static_cast<int64_t>(c0) * f.qs[2], f.qs[2], kC, tid);
+        load_tile_async<T, D, kThreads>(b2, gbase + static_cast<int64_t>(c0) * p.dos[2], p.dos[2], kC, tid);
+        if (tid < kC) {
+          c_stat[buf * 2 * kC + tid] = f.lse[stat0 + c0 + tid] * kLog2e;
+          c_stat[buf * 2 * kC + kC + tid] = p.dsum[stat0 + c0 + tid];
+        }
+      }
+      if (masked && mask_vec) {
+        // the chunk's mask bytes, [query row][kv row]: R x 32 (mode 0) or 32 x R (mode 1)
+        constexpr int kQ = MODE == 0 ? R : kC, kK = MODE == 0 ? kC : R;
+        const int q0 = MODE == 0 ? row0 : c0, k0 = MODE == 0 ? c0 : row0;
+        uint8_t* dstm = s_mask + static_cast<size_t>(buf) * R * kC;
+        for (int e = tid; e < kQ * (kK / 16); e += kThreads) {
+          const int qr = e / (kK / 16), piece = e % (kK / 16);
+          cp_async_16(dstm + qr * kK + piece * 16, mbase + static_cast<int64_t>(q0 + qr) * f.ms[2] + k0 + piece * 16);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
   // the CTA's own rows: Q and dO (mode 0), K and V (mode 1)
   if (MODE == 0) {
-    load_tile<T, D>(sA1, qbase + static_cast<int64_t>(row0) * f.qs[2], f.qs[2], tid);
-    load_tile<T, D>(sA2, gbase + static_cast<int64_t>(row0) * p.dos[2], p.dos[2], tid);
+    load_tile_async<T, D, kThreads>(sA1, qbase + static_cast<int64_t>(row0) * f.qs[2], f.qs[2], R, tid);
+    load_tile_async<T, D, kThreads>(sA2, gbase + static_cast<int64_t>(row0) * p.dos[2], p.dos[2], R, tid);
     // D_i = sum_d dO_id O_id (- d_lse_i): two threads per row
     const int r = tid >> 1, half = tid & 1;
     const T* o = static_cast<const T*>(f.o) + b * f.os[0] + h * f.os[1] + static_cast<int64_t>(row0 + r) * f.os[2];
@@ -129,9 +204,10 @@ attn_bwd_mma_kernel(const AttnBwdParams p) {
       s_lse2[r] = f.lse[stat] * kLog2e;              // -inf for a row with no attended key: no gradient
     }
   } else {
-    load_tile<T, D>(sA1, kbase + static_cast<int64_t>(row0) * f.ks[2], f.ks[2], tid);
-    load_tile<T, D>(sA2, vbase + static_cast<int64_t>(row0) * f.vs[2], f.vs[2], tid);
+    load_tile_async<T, D, kThreads>(sA1, kbase + static_cast<int64_t>(row0) * f.ks[2], f.ks[2], R, tid);
+    load_tile_async<T, D, kThreads>(sA2, vbase + static_cast<int64_t>(row0) * f.vs[2], f.vs[2], R, tid);
   }
+  cp_async_commit();
 
   // accumulators of this warp's 16 rows: dQ (mode 0); dV and dK (mode 1)
   wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc1[D / 16];
@@ -146,117 +222,98 @@ attn_bwd_mma_kernel(const AttnBwdParams p) {
   const T* a1_w = sA1 + warp * 16 * kLd;
   const T* a2_w = sA2 + warp * 16 * kLd;
 
+  if (total_chunks > 0) request(0);
 #pragma unroll 1
-  for (int pass = 0; pass < 2; ++pass) {
-    const bool masked = pass == 1;
-    const int32_t* ids;
-    int64_t id_stride;
-    int n_given;
-    if (MODE == 0) {
-      ids = masked ? f.part_ids + b * f.pis[0] + h * f.pis[1] + static_cast<int64_t>(own_blk) * f.pis[2]
-                   : f.full_ids + b * f.fis[0] + h * f.fis[1] + static_cast<int64_t>(own_blk) * f.fis[2];
-      id_stride = masked ? f.pis[3] : f.fis[3];
-      n_given = masked ? f.part_lens[b * f.pls[0] + h * f.pls[1] + static_cast<int64_t>(own_blk) * f.pls[2]]
-                       : f.full_lens[b * f.fls[0] + h * f.fls[1] + static_cast<int64_t>(own_blk) * f.fls[2]];
+  for (int u = 0; u < total_chunks; ++u) {
+    // the next chunk travels while this one is worked on
+    if (u + 1 < total_chunks) { request(u + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    bool masked;
+    const int c0 = chunk_of(u, masked);
+    const int buf = u & 1;
+    if (c0 < 0) {
+      if (tid == 0 && f.dev_status != nullptr) atomicMax(f.dev_status, SA_DEV_BAD_INDEX);
     } else {
-      ids = masked ? p.t_part_ids + b * p.tpis[0] + h * p.tpis[1] + static_cast<int64_t>(own_blk) * p.tpis[2]
-                   : p.t_full_ids + b * p.tfis[0] + h * p.tfis[1] + static_cast<int64_t>(own_blk) * p.tfis[2];
-      id_stride = masked ? p.tpis[3] : p.tfis[3];
-      n_given = masked ? p.t_part_lens[b * p.tpls[0] + h * p.tpls[1] + static_cast<int64_t>(own_blk) * p.tpls[2]]
-                       : p.t_full_lens[b * p.tfls[0] + h * p.tfls[1] + static_cast<int64_t>(own_blk) * p.tfls[2]];
-    }
-    const int n = min(max(n_given, 0), n_other);
-#pragma unroll 1
-    for (int t = 0; t < n; ++t) {
-      const int id = ids[t * id_stride];
-      if (id < 0 || id >= n_other) {
-        if (tid == 0 && f.dev_status != nullptr) atomicMax(f.dev_status, SA_DEV_BAD_INDEX);
-        continue;
+      const T* sB1 = sB + static_cast<size_t>(buf) * 2 * kC * kLd;
+      const T* sB2 = sB1 + kC * kLd;
+      // T1 = A1_w . B1^T and T2 = A2_w . B2^T (16 x 32 each, over the head dim) into this warp's scratch
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const T* a_w = which == 0 ? a1_w : a2_w;
+        const T* bt = which == 0 ? sB1 : sB2;
+        wmma::fragment<wmma::accumulator, 16, 16, 16, float> c[kC / 16];
+#pragma unroll
+        for (int nfr = 0; nfr < kC / 16; ++nfr) wmma::fill_fragment(c[nfr], 0.f);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> a;
+          wmma::load_matrix_sync(a, a_w + kk * 16, kLd);
+#pragma unroll
+          for (int nfr = 0; nfr < kC / 16; ++nfr) {
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> bm;
+            wmma::load_matrix_sync(bm, bt + nfr * 16 * kLd + kk * 16, kLd);     // (k, n) = B[n][k]
+            wmma::mma_sync(c[nfr], a, bm, c[nfr]);
+          }
+        }
+#pragma unroll
+        for (int nfr = 0; nfr < kC / 16; ++nfr)
+          wmma::store_matrix_sync(sT + which * 16 * kLdT + nfr * 16, c[nfr], kLdT, wmma::mem_row_major);
       }
-#pragma unroll 1
-      for (int sub = 0; sub < other_rows; sub += kC) {
-        const int c0 = id * other_rows + sub;           // first row of the chunk on the other side
-        __syncthreads();                                // every warp is done with the previous chunk's tiles
-        if (MODE == 0) {
-          load_tile<T, D>(sB1, kbase + static_cast<int64_t>(c0) * f.ks[2], f.ks[2], tid);
-          load_tile<T, D>(sB2, vbase + static_cast<int64_t>(c0) * f.vs[2], f.vs[2], tid);
-        } else {
-          load_tile<T, D>(sB1, qbase + static_cast<int64_t>(c0) * f.qs[2], f.qs[2], tid);
-          load_tile<T, D>(sB2, gbase + static_cast<int64_t>(c0) * p.dos[2], p.dos[2], tid);
-          if (tid < kC) {
-            c_lse2[tid] = f.lse[stat0 + c0 + tid] * kLog2e;
-            c_dsum[tid] = p.dsum[stat0 + c0 + tid];
-          }
-        }
-        __syncthreads();
+      __syncwarp();
 
-        // T1 = A1_w . B1^T and T2 = A2_w . B2^T (16 x 32 each, over the head dim) into this warp's scratch
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          const T* a_w = which == 0 ? a1_w : a2_w;
-          const T* bt = which == 0 ? sB1 : sB2;
-#pragma unroll
-          for (int nf = 0; nf < kC / 16; ++nf) {
-            wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-            wmma::fill_fragment(c, 0.f);
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-              wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> a;
-              wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> bm;
-              wmma::load_matrix_sync(a, a_w + kk * 16, kLd);
-              wmma::load_matrix_sync(bm, bt + nf * 16 * kLd + kk * 16, kLd);     // (k, n) = B[n][k]
-              wmma::mma_sync(c, a, bm, c);
-            }
-            wmma::store_matrix_sync(sT + which * 16 * kLdT + nf * 16, c, kLdT, wmma::mem_row_major);
-          }
-        }
-        __syncwarp();
-
-        // P and dS, element by element: lane = column of the chunk, 16 rows each
-        {
-          const int col = lane;
+      // P and dS, element by element: lane = column of the chunk, 16 rows each
+      {
+        const int col = lane;
+        const uint8_t* sm = s_mask + static_cast<size_t>(buf) * R * kC;
+        const float* cs = c_stat + buf * 2 * kC;
 #pragma unroll 4
-          for (int i = 0; i < 16; ++i) {
-            const int r = warp * 16 + i;                 // row of the CTA
-            const float t1 = sT[i * kLdT + col], t2 = sT[16 * kLdT + i * kLdT + col];
-            float lse2, dsum;
-            int qrow, krow;
-            if (MODE == 0) { lse2 = s_lse2[r]; dsum = s_dsum[r]; qrow = row0 + r; krow = c0 + col; }
-            else           { lse2 = c_lse2[col]; dsum = c_dsum[col]; qrow = c0 + col; krow = row0 + r; }
-            bool attend = lse2 > -INFINITY;
-            if (masked && attend)
-              attend = mbase[static_cast<int64_t>(qrow) * f.ms[2] + static_cast<int64_t>(krow) * f.ms[3]] != 0;
-            const float pe = attend ? exp2f(t1 * f.scale_log2 - lse2) : 0.f;
-            const float ds = pe * (t2 - dsum);
-            sE[i * kLdE + col] = from_float<T>(pe);
-            sE[16 * kLdE + i * kLdE + col] = from_float<T>(ds);
-          }
-        }
-        __syncwarp();
-
-        // mode 0: dQ_w += dS . K_chunk; mode 1: dV_w += P^T-rows . dO_chunk, dK_w += dS . Q_chunk
-#pragma unroll
-        for (int kk = 0; kk < kC / 16; ++kk) {
-          wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> e_p, e_ds;
-          wmma::load_matrix_sync(e_ds, sE + 16 * kLdE + kk * 16, kLdE);
-          if (MODE == 1) wmma::load_matrix_sync(e_p, sE + kk * 16, kLdE);
-#pragma unroll
-          for (int nf = 0; nf < D / 16; ++nf) {
-            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> b1;
-            wmma::load_matrix_sync(b1, sB1 + kk * 16 * kLd + nf * 16, kLd);
-            if constexpr (MODE == 0) {
-              wmma::mma_sync(acc1[nf], e_ds, b1, acc1[nf]);
+        for (int i = 0; i < 16; ++i) {
+          const int r = warp * 16 + i;                 // row of the CTA
+          const float t1 = sT[i * kLdT + col], t2 = sT[16 * kLdT + i * kLdT + col];
+          float lse2, dsum;
+          if (MODE == 0) { lse2 = s_lse2[r]; dsum = s_dsum[r]; }
+          else           { lse2 = cs[col]; dsum = cs[kC + col]; }
+          bool attend = lse2 > -INFINITY;
+          if (masked && attend) {
+            if (mask_vec) {
+              attend = (MODE == 0 ? sm[r * kC + col] : sm[col * R + r]) != 0;
             } else {
-              wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> b2;
-              wmma::load_matrix_sync(b2, sB2 + kk * 16 * kLd + nf * 16, kLd);
-              wmma::mma_sync(acc1[nf], e_p, b2, acc1[nf]);        // dV
-              wmma::mma_sync(acc2[nf], e_ds, b1, acc2[nf]);       // dK
+              const int qrow = MODE == 0 ? row0 + r : c0 + col, krow = MODE == 0 ? c0 + col : row0 + r;
+              attend = mbase[static_cast<int64_t>(qrow) * f.ms[2] + static_cast<int64_t>(krow) * f.ms[3]] != 0;
             }
+          }
+          const float pe = attend ? exp2f(t1 * f.scale_log2 - lse2) : 0.f;
+          const float ds = pe * (t2 - dsum);
+          sE[i * kLdE + col] = from_float<T>(pe);
+          sE[16 * kLdE + i * kLdE + col] = from_float<T>(ds);
+        }
+      }
+      __syncwarp();
+
+      // mode 0: dQ_w += dS . K_chunk; mode 1: dV_w += P . dO_chunk, dK_w += dS . Q_chunk
+#pragma unroll
+      for (int kk = 0; kk < kC / 16; ++kk) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> e_p, e_ds;
+        wmma::load_matrix_sync(e_ds, sE + 16 * kLdE + kk * 16, kLdE);
+        if (MODE == 1) wmma::load_matrix_sync(e_p, sE + kk * 16, kLdE);
+#pragma unroll
+        for (int nfr = 0; nfr < D / 16; ++nfr) {
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> b1;
+          wmma::load_matrix_sync(b1, sB1 + kk * 16 * kLd + nfr * 16, kLd);
+          if constexpr (MODE == 0) {
+            wmma::mma_sync(acc1[nfr], e_ds, b1, acc1[nfr]);
+          } else {
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> b2;
+            wmma::load_matrix_sync(b2, sB2 + kk * 16 * kLd + nfr * 16, kLd);
+            wmma::mma_sync(acc1[nfr], e_p, b2, acc1[nfr]);        // dV
+            wmma::mma_sync(acc2[nfr], e_ds, b1, acc2[nfr]);       // dK
           }
         }
       }
     }
+    __syncthreads();                                // every warp is done with this buffer before it is requested again
   }
+  cp_async_wait<0>();
 
   // write the warp's 16 rows out, 16 columns at a time, through its scratch
   const float scale = f.scale_log2 * kLn2;
@@ -264,15 +321,15 @@ attn_bwd_mma_kernel(const AttnBwdParams p) {
   auto write_out = [&](wmma::fragment<wmma::accumulator, 16, 16, 16, float>* acc, T* out_base, int64_t row_stride,
                        float factor) {
 #pragma unroll
-    for (int nf = 0; nf < D / 16; ++nf) {
-      wmma::store_matrix_sync(sT, acc[nf], kLdT, wmma::mem_row_major);
+    for (int nfr = 0; nfr < D / 16; ++nfr) {
+      wmma::store_matrix_sync(sT, acc[nfr], kLdT, wmma::mem_row_major);
       __syncwarp();
       const int r = lane >> 1, c8 = (lane & 1) * 8;        // 16 rows x two halves of 8 columns
       const float* src = sT + r * kLdT + c8;
       T vals[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) vals[i] = from_float<T>(src[i] * factor);
-      *reinterpret_cast<uint4*>(out_base + static_cast<int64_t>(warp * 16 + r) * row_stride + nf * 16 + c8) =
+      *reinterpret_cast<uint4*>(out_base + static_cast<int64_t>(warp * 16 + r) * row_stride + nfr * 16 + c8) =
           *reinterpret_cast<const uint4*>(vals);
       __syncwarp();
     }
@@ -292,30 +349,42 @@ bool vec_ok(const void* base, const int64_t* st) {
   return reinterpret_cast<uintptr_t>(base) % 16 == 0 && st[3] == 1 && st[2] % 8 == 0 && st[1] % 8 == 0 && st[0] % 8 == 0;
 }
 
-template <typename T, int D>
-cudaError_t launch_both(const AttnBwdParams& p, cudaStream_t stream) {
+template <typename T, int D, int R, int MODE>
+cudaError_t launch_one(const AttnBwdParams& p, int mask_vec, cudaStream_t stream) {
   const AttnParams& f = p.fwd;
   const DeviceInfo* info = current_device_info();
   if (info == nullptr) return cudaErrorNoDevice;
-  auto k0 = attn_bwd_mma_kernel<T, D, 0>;
-  auto k1 = attn_bwd_mma_kernel<T, D, 1>;
-  constexpr size_t smem = BwdSmem<D>::total;
+  auto kernel = attn_bwd_mma_kernel<T, D, R, MODE>;
+  constexpr size_t smem = BwdSmem<D, R>::total;
   static std::once_flag once[kMaxDevices];
   static cudaError_t attr[kMaxDevices];
   std::call_once(once[info->ordinal], [&] {
-    cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    attr[info->ordinal] = e;
+    attr[info->ordinal] = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   });
   if (attr[info->ordinal] != cudaSuccess) return attr[info->ordinal];
-  const long long ctas_q = static_cast<long long>(f.Sq / kR) * f.B * f.H;
-  const long long ctas_k = static_cast<long long>(f.Sk / kR) * f.B * f.H;
-  if (ctas_q <= 0 || ctas_k <= 0 || ctas_q > 0x7fffffffLL || ctas_k > 0x7fffffffLL) return cudaErrorInvalidValue;
-  k0<<<static_cast<unsigned>(ctas_q), kThreadsMma, smem, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  k1<<<static_cast<unsigned>(ctas_k), kThreadsMma, smem, stream>>>(p);          // reads D from the first
+  const long long ctas = static_cast<long long>((MODE == 0 ? f.Sq : f.Sk) / R) * f.B * f.H;
+  if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidValue;
+  kernel<<<static_cast<unsigned>(ctas), 2 * R, smem, stream>>>(p, mask_vec);
   return cudaGetLastError();
+}
+
+// rows per CTA: the largest of 128 / 64 / 32 that divides the block size of the CTA's side
+template <typename T, int D, int MODE>
+cudaError_t launch_mode(const AttnBwdParams& p, int mask_vec, cudaStream_t stream) {
+  const int blk = MODE == 0 ? p.fwd.BQ : p.fwd.BK;
+  if (blk % 64 == 0) return launch_one<T, D, 64, MODE>(p, mask_vec, stream);
+  return launch_one<T, D, 32, MODE>(p, mask_vec, stream);
+}
+
+template <typename T, int D>
+cudaError_t launch_both(const AttnBwdParams& p, cudaStream_t stream) {
+  const AttnParams& f = p.fwd;
+  // the mask chunks are staged with 16-byte copies when its rows allow it
+  const int mask_vec = reinterpret_cast<uintptr_t>(f.mask) % 16 == 0 && f.ms[3] == 1 && f.ms[2] % 16 == 0 &&
+                       f.ms[1] % 16 == 0 && f.ms[0] % 16 == 0;
+  cudaError_t e = launch_mode<T, D, 0>(p, mask_vec, stream);
+  if (e != cudaSuccess) return e;
+  return launch_mode<T, D, 1>(p, mask_vec, stream);           // reads D from the first
 }
 
 }  // namespace
