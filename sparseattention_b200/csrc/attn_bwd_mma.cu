@@ -14,12 +14,13 @@
 //   mode 1 (dK, dV): a CTA owns 32 kv rows and walks the transposed (kv-major) lists of their kv block.
 // In both the other side arrives in chunks of 32 rows staged in shared memory.  A warp owns 16 of the
 // CTA's rows and needs nothing from the other warp: per chunk it forms two 16 x 32 products over the
-// head dim (scores and dO.V^T), turns them into P and dS element by element through shared memory
-// (rounded to the input type, as the forward rounds P before P.V), and accumulates 16 x D products
-// over the chunk's 32 rows.
+// head dim (scores and dO.V^T; mma.sync m16n8k16, operands by ldmatrix), turns them into P and dS in
+// its registers (rounded to the input type, as the forward rounds P before P.V: two adjacent 8-column
+// accumulator tiles are one 16-column A operand), and accumulates 16 x D products over the chunk's 32
+// rows.  The chunks are requested one ahead with cp.async (two buffers), the mask bytes of partial
+// blocks with them.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <mma.h>
 
 #include <mutex>
 
@@ -28,33 +29,23 @@
 namespace sa {
 namespace {
 
-using namespace nvcuda;
-
 constexpr int kC = 32;            // rows of the other side per chunk
-constexpr int kLdT = kC + 4;      // fp32 scratch rows (floats)
-constexpr int kLdE = kC + 8;      // P / dS rows (elements)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // R = rows a CTA owns (32, 64 or 128: never more than the block size of its side, so that all of them
 // walk the same lists); a warp owns 16 of them.
 template <int D, int R> struct BwdSmem {
-  static constexpr int kWarps = R / 16;
   static constexpr int kLd = D + 8;                                 // rows of the staged tiles (elements): 16 bytes of padding
   static constexpr size_t tile_a = static_cast<size_t>(R) * kLd * 2;          // bytes of one R x D tile
   static constexpr size_t tile_b = static_cast<size_t>(kC) * kLd * 2;         // bytes of one 32 x D tile
   static constexpr size_t off_a1 = 0, off_a2 = tile_a;
   static constexpr size_t off_b = 2 * tile_a;                                 // [2 buffers][2 tiles]
-  static constexpr size_t off_t = off_b + 4 * tile_b;                         // [warp][2][16][kLdT] float
-  static constexpr size_t off_e = off_t + static_cast<size_t>(kWarps) * 2 * 16 * kLdT * 4;   // [warp][2][16][kLdE] T
-  static constexpr size_t off_mask = off_e + static_cast<size_t>(kWarps) * 2 * 16 * kLdE * 2;  // [2 buffers][R * 32] bytes
+  static constexpr size_t off_mask = off_b + 4 * tile_b;                      // [2 buffers][R * 32] bytes
   static constexpr size_t off_stat = off_mask + 2 * static_cast<size_t>(R) * kC;             // own lse2[R], dsum[R]; chunk's [2][2][32]
   static constexpr size_t total = off_stat + (2 * R + 4 * kC) * 4;
 };
 
-template <typename T> __device__ __forceinline__ T from_float(float x);
-template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
-template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <typename T> __device__ __forceinline__ float to_float(T x);
 template <> __device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
@@ -66,6 +57,50 @@ __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// four 8 x 8 matrices of 16-bit elements from shared memory; lane l gives the address of row l % 8 of
+// matrix l / 8; register i of a lane holds elements (row lane / 4, columns 2 * (lane % 4) + {0, 1}) of
+// matrix i -- of its transpose with kTrans
+template <bool kTrans>
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+  if (kTrans)
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+  else
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+// D (16 x 8, fp32) += A (16 x 16, row) . B (16 x 8, col).  With g = lane / 4, t = lane % 4:
+// A: a0 (row g, k 2t..), a1 (row g+8, k 2t..), a2 (row g, k 2t+8..), a3 (row g+8, k 2t+8..);
+// B: b0 (k 2t.., n g), b1 (k 2t+8.., n g);  D: d0 d1 (row g, n 2t 2t+1), d2 d3 (row g+8, n 2t 2t+1).
+template <typename T>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma_16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma_16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // `rows` rows x D elements from global memory (unit stride along D, 16-byte aligned rows) into a padded
@@ -97,8 +132,6 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
   const AttnParams& f = p.fwd;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  float* sT = reinterpret_cast<float*>(smem + S::off_t) + warp * 2 * 16 * kLdT;
-  T* sE = reinterpret_cast<T*>(smem + S::off_e) + warp * 2 * 16 * kLdE;
 
   const int rows_total = MODE == 0 ? f.Sq : f.Sk;
   const int groups = rows_total / R;
@@ -209,18 +242,28 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
   }
   cp_async_commit();
 
-  // accumulators of this warp's 16 rows: dQ (mode 0); dV and dK (mode 1)
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc1[D / 16];
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc2[MODE == 1 ? D / 16 : 1];
+  // Accumulators of this warp's 16 rows, as 16 x 8 tiles of the MMA: dQ (mode 0); dV and dK (mode 1).
+  constexpr int kDT = D / 8;
+  float acc1[kDT][4];
+  float acc2[MODE == 1 ? kDT : 1][4];
 #pragma unroll
-  for (int n = 0; n < D / 16; ++n) wmma::fill_fragment(acc1[n], 0.f);
+  for (int n = 0; n < kDT; ++n) { acc1[n][0] = acc1[n][1] = acc1[n][2] = acc1[n][3] = 0.f; }
   if constexpr (MODE == 1) {
 #pragma unroll
-    for (int n = 0; n < D / 16; ++n) wmma::fill_fragment(acc2[n], 0.f);
+    for (int n = 0; n < kDT; ++n) { acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f; }
   }
 
-  const T* a1_w = sA1 + warp * 16 * kLd;
-  const T* a2_w = sA2 + warp * 16 * kLd;
+  const int g = lane >> 2, t4 = lane & 3;
+  // ldmatrix addresses: A operand (this warp's rows, k along the head dim): row lane % 16, +8 columns for lanes >= 16
+  const T* a1_ld = sA1 + (warp * 16 + (lane & 15)) * kLd + (lane >> 4) * 8;
+  const T* a2_ld = sA2 + (warp * 16 + (lane & 15)) * kLd + (lane >> 4) * 8;
+  // B operand of the first products, B(k, n) = tile[n][k] (no transpose): matrices (n 0-7, k 0-7), (n 0-7, k 8-15),
+  // (n 8-15, k 0-7), (n 8-15, k 8-15)
+  const int bt_row = ((lane >> 4) << 3) + (lane & 7), bt_col = ((lane >> 3) & 1) * 8;
+  // B operand of the accumulating products, B(k, n) = tile[k][n] (transposed load): matrices (k 0-7, n 0-7),
+  // (k 8-15, n 0-7), (k 0-7, n 8-15), (k 8-15, n 8-15)
+  const int bn_row = (((lane >> 3) & 1) << 3) + (lane & 7), bn_col = (lane >> 4) * 8;
+  float own_lse2[2] = {0.f, 0.f}, own_dsum[2] = {0.f, 0.f};
 
   if (total_chunks > 0) request(0);
 #pragma unroll 1
@@ -228,6 +271,13 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
     // the next chunk travels while this one is worked on
     if (u + 1 < total_chunks) { request(u + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
     __syncthreads();
+    if (MODE == 0 && u == 0) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        own_lse2[hh] = s_lse2[warp * 16 + g + 8 * hh];
+        own_dsum[hh] = s_dsum[warp * 16 + g + 8 * hh];
+      }
+    }
     bool masked;
     const int c0 = chunk_of(u, masked);
     const int buf = u & 1;
@@ -236,42 +286,41 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
     } else {
       const T* sB1 = sB + static_cast<size_t>(buf) * 2 * kC * kLd;
       const T* sB2 = sB1 + kC * kLd;
-      // T1 = A1_w . B1^T and T2 = A2_w . B2^T (16 x 32 each, over the head dim) into this warp's scratch
+      // T1 = A1_w . B1^T (scores) and T2 = A2_w . B2^T (16 x 32 each, over the head dim), in registers
+      float t1[kC / 8][4], t2[kC / 8][4];
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const T* a_w = which == 0 ? a1_w : a2_w;
-        const T* bt = which == 0 ? sB1 : sB2;
-        wmma::fragment<wmma::accumulator, 16, 16, 16, float> c[kC / 16];
-#pragma unroll
-        for (int nfr = 0; nfr < kC / 16; ++nfr) wmma::fill_fragment(c[nfr], 0.f);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> a;
-          wmma::load_matrix_sync(a, a_w + kk * 16, kLd);
-#pragma unroll
-          for (int nfr = 0; nfr < kC / 16; ++nfr) {
-            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> bm;
-            wmma::load_matrix_sync(bm, bt + nfr * 16 * kLd + kk * 16, kLd);     // (k, n) = B[n][k]
-            wmma::mma_sync(c[nfr], a, bm, c[nfr]);
-          }
-        }
-#pragma unroll
-        for (int nfr = 0; nfr < kC / 16; ++nfr)
-          wmma::store_matrix_sync(sT + which * 16 * kLdT + nfr * 16, c[nfr], kLdT, wmma::mem_row_major);
+      for (int n = 0; n < kC / 8; ++n) {
+        t1[n][0] = t1[n][1] = t1[n][2] = t1[n][3] = 0.f;
+        t2[n][0] = t2[n][1] = t2[n][2] = t2[n][3] = 0.f;
       }
-      __syncwarp();
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a1[4], a2[4];
+        ldmatrix_x4<false>(a1, a1_ld + kk * 16);
+        ldmatrix_x4<false>(a2, a2_ld + kk * 16);
+#pragma unroll
+        for (int np = 0; np < kC / 16; ++np) {          // pairs of 8-column tiles
+          uint32_t b1[4], b2[4];
+          ldmatrix_x4<false>(b1, sB1 + (np * 16 + bt_row) * kLd + kk * 16 + bt_col);
+          ldmatrix_x4<false>(b2, sB2 + (np * 16 + bt_row) * kLd + kk * 16 + bt_col);
+          mma_16816<T>(t1[2 * np], a1, b1[0], b1[1]);
+          mma_16816<T>(t1[2 * np + 1], a1, b1[2], b1[3]);
+          mma_16816<T>(t2[2 * np], a2, b2[0], b2[1]);
+          mma_16816<T>(t2[2 * np + 1], a2, b2[2], b2[3]);
+        }
+      }
 
-      // P and dS, element by element: lane = column of the chunk, 16 rows each
-      {
-        const int col = lane;
-        const uint8_t* sm = s_mask + static_cast<size_t>(buf) * R * kC;
-        const float* cs = c_stat + buf * 2 * kC;
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-          const int r = warp * 16 + i;                 // row of the CTA
-          const float t1 = sT[i * kLdT + col], t2 = sT[16 * kLdT + i * kLdT + col];
+      // P and dS in place: element (row g + 8 * (i / 2), column 8 * n + 2 * t4 + (i & 1)) of the chunk
+      const uint8_t* sm = s_mask + static_cast<size_t>(buf) * R * kC;
+      const float* cs = c_stat + buf * 2 * kC;
+#pragma unroll
+      for (int n = 0; n < kC / 8; ++n) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = warp * 16 + g + 8 * (i >> 1);    // row of the CTA
+          const int col = 8 * n + 2 * t4 + (i & 1);      // column of the chunk
           float lse2, dsum;
-          if (MODE == 0) { lse2 = s_lse2[r]; dsum = s_dsum[r]; }
+          if (MODE == 0) { lse2 = own_lse2[i >> 1]; dsum = own_dsum[i >> 1]; }
           else           { lse2 = cs[col]; dsum = cs[kC + col]; }
           bool attend = lse2 > -INFINITY;
           if (masked && attend) {
@@ -282,31 +331,41 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
               attend = mbase[static_cast<int64_t>(qrow) * f.ms[2] + static_cast<int64_t>(krow) * f.ms[3]] != 0;
             }
           }
-          const float pe = attend ? exp2f(t1 * f.scale_log2 - lse2) : 0.f;
-          const float ds = pe * (t2 - dsum);
-          sE[i * kLdE + col] = from_float<T>(pe);
-          sE[16 * kLdE + i * kLdE + col] = from_float<T>(ds);
+          const float pe = attend ? exp2f(t1[n][i] * f.scale_log2 - lse2) : 0.f;
+          t1[n][i] = pe;
+          t2[n][i] = pe * (t2[n][i] - dsum);
         }
       }
-      __syncwarp();
 
-      // mode 0: dQ_w += dS . K_chunk; mode 1: dV_w += P . dO_chunk, dK_w += dS . Q_chunk
+      // mode 0: dQ_w += dS . K_chunk; mode 1: dV_w += P . dO_chunk, dK_w += dS . Q_chunk.  Two adjacent 8-column
+      // tiles of the first products are one 16-column A operand of these (rounded to the input type).
 #pragma unroll
-      for (int kk = 0; kk < kC / 16; ++kk) {
-        wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> e_p, e_ds;
-        wmma::load_matrix_sync(e_ds, sE + 16 * kLdE + kk * 16, kLdE);
-        if (MODE == 1) wmma::load_matrix_sync(e_p, sE + kk * 16, kLdE);
+      for (int ks = 0; ks < kC / 16; ++ks) {
+        uint32_t e_p[4], e_ds[4];
+        e_ds[0] = pack_pair<T>(t2[2 * ks][0], t2[2 * ks][1]);
+        e_ds[1] = pack_pair<T>(t2[2 * ks][2], t2[2 * ks][3]);
+        e_ds[2] = pack_pair<T>(t2[2 * ks + 1][0], t2[2 * ks + 1][1]);
+        e_ds[3] = pack_pair<T>(t2[2 * ks + 1][2], t2[2 * ks + 1][3]);
+        if (MODE == 1) {
+          e_p[0] = pack_pair<T>(t1[2 * ks][0], t1[2 * ks][1]);
+          e_p[1] = pack_pair<T>(t1[2 * ks][2], t1[2 * ks][3]);
+          e_p[2] = pack_pair<T>(t1[2 * ks + 1][0], t1[2 * ks + 1][1]);
+          e_p[3] = pack_pair<T>(t1[2 * ks + 1][2], t1[2 * ks + 1][3]);
+        }
 #pragma unroll
-        for (int nfr = 0; nfr < D / 16; ++nfr) {
-          wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> b1;
-          wmma::load_matrix_sync(b1, sB1 + kk * 16 * kLd + nfr * 16, kLd);
+        for (int dp = 0; dp < D / 16; ++dp) {           // pairs of 8-column tiles of the head dim
+          uint32_t b1[4];
+          ldmatrix_x4<true>(b1, sB1 + (ks * 16 + bn_row) * kLd + dp * 16 + bn_col);
           if constexpr (MODE == 0) {
-            wmma::mma_sync(acc1[nfr], e_ds, b1, acc1[nfr]);
+            mma_16816<T>(acc1[2 * dp], e_ds, b1[0], b1[1]);
+            mma_16816<T>(acc1[2 * dp + 1], e_ds, b1[2], b1[3]);
           } else {
-            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> b2;
-            wmma::load_matrix_sync(b2, sB2 + kk * 16 * kLd + nfr * 16, kLd);
-            wmma::mma_sync(acc1[nfr], e_p, b2, acc1[nfr]);        // dV
-            wmma::mma_sync(acc2[nfr], e_ds, b1, acc2[nfr]);       // dK
+            uint32_t b2[4];
+            ldmatrix_x4<true>(b2, sB2 + (ks * 16 + bn_row) * kLd + dp * 16 + bn_col);
+            mma_16816<T>(acc1[2 * dp], e_p, b2[0], b2[1]);          // dV
+            mma_16816<T>(acc1[2 * dp + 1], e_p, b2[2], b2[3]);
+            mma_16816<T>(acc2[2 * dp], e_ds, b1[0], b1[1]);         // dK
+            mma_16816<T>(acc2[2 * dp + 1], e_ds, b1[2], b1[3]);
           }
         }
       }
@@ -315,23 +374,16 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
   }
   cp_async_wait<0>();
 
-  // write the warp's 16 rows out, 16 columns at a time, through its scratch
+  // write the warp's 16 rows out: a lane holds columns 8 * n + 2 * t4 + {0, 1} of rows g and g + 8
   const float scale = f.scale_log2 * kLn2;
-  __syncwarp();
-  auto write_out = [&](wmma::fragment<wmma::accumulator, 16, 16, 16, float>* acc, T* out_base, int64_t row_stride,
-                       float factor) {
+  auto write_out = [&](float (*acc)[4], T* out_base, int64_t row_stride, float factor) {
 #pragma unroll
-    for (int nfr = 0; nfr < D / 16; ++nfr) {
-      wmma::store_matrix_sync(sT, acc[nfr], kLdT, wmma::mem_row_major);
-      __syncwarp();
-      const int r = lane >> 1, c8 = (lane & 1) * 8;        // 16 rows x two halves of 8 columns
-      const float* src = sT + r * kLdT + c8;
-      T vals[8];
+    for (int n = 0; n < kDT; ++n) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) vals[i] = from_float<T>(src[i] * factor);
-      *reinterpret_cast<uint4*>(out_base + static_cast<int64_t>(warp * 16 + r) * row_stride + nfr * 16 + c8) =
-          *reinterpret_cast<const uint4*>(vals);
-      __syncwarp();
+      for (int hh = 0; hh < 2; ++hh) {
+        T* dst = out_base + static_cast<int64_t>(warp * 16 + g + 8 * hh) * row_stride + 8 * n + 2 * t4;
+        *reinterpret_cast<uint32_t*>(dst) = pack_pair<T>(acc[n][2 * hh] * factor, acc[n][2 * hh + 1] * factor);
+      }
     }
   };
   if constexpr (MODE == 0) {
