@@ -209,9 +209,11 @@ size_t sa_attn_bwd_workspace_bytes(int B, int H, int Sq);
 /* No counterpart in the reference.  Gradients of sa_attn_fwd with respect to q, k and v over the same
  * lists: P is recomputed from lse (the forward's optional output; a row whose lse is -inf has no
  * gradient), dV = P^T dO, dS = P * (dO V^T - D), dQ = scale dS K, dK = scale dS^T Q, with
- * D = rowsum(dO * O) - d_lse.  CUDA-core kernels, fp32 math, any of the three dtypes, D in
- * {16, 32, 64, 128}, block sizes that are multiples of 32; no atomics (the result does not depend on
- * scheduling).
+ * D = rowsum(dO * O) - d_lse.  Any of the three dtypes, D in {16, 32, 64, 128}, block sizes that are
+ * multiples of 32; no atomics (the result does not depend on scheduling).  fp16 / bf16 with D = 64 or
+ * 128, unit stride along D and 16-byte aligned rows in every tensor run on the tensor cores (fp32
+ * accumulation, P and dS rounded to the input type like the forward's P); everything else on the CUDA
+ * cores in fp32.
  * o, d_o: the forward's output and its incoming gradient, [B,H,Sq,D] with element strides; lse: float32
  *   [B,H,Sq] contiguous from the forward; d_lse: optional incoming gradient of lse, same layout, or NULL.
  * dq, dk, dv: outputs with element strides, dtype of q.
