@@ -127,3 +127,25 @@ def test_backward_op_passes_opcheck(native_lib):
     args = (q, k, v, o, torch.ones_like(o), lse, None, mask.expand(B, H, S, S), ex(f_ids), ex(f_lens), ex(p_ids),
             ex(p_lens), ex(t[0]), ex(t[1]), ex(t[2]), ex(t[3]), 128, 32)
     torch.library.opcheck(_native.attn_bwd_op, args, test_utils=("test_schema", "test_faketensor"))
+
+
+@pytest.mark.parametrize("dtype,D,bq,bk", [(torch.bfloat16, 128, 64, 64), (torch.float16, 128, 128, 128),
+                                          (torch.bfloat16, 64, 32, 32)])
+def test_tensor_core_backward_on_a_mask_with_unaligned_rows(native_lib, dtype, D, bq, bk):
+    """The tensor-core backward kernels with 64 and 32 rows per CTA on either side, and a mask whose rows
+    are not 16-byte aligned (a view into a wider buffer): the mask bytes are then read one by one."""
+    B, H, S = 1, 3, 768
+    q, k, v = workloads.make_qkv(B, H, S, D, dtype, seed=330 + bq)
+    wide = torch.zeros((B, 1, S, S + 8), dtype=torch.bool)
+    wide[..., 4:S + 4] = workloads.document_causal_mask(B, S, (90, 300), 0.15, seed=331 + bk)
+    mask = wide[..., 4:S + 4]
+    g = torch.Generator().manual_seed(9)
+    w = torch.randn((B, H, S, D), generator=g).to(dtype)
+    want = _reference_grads(q, k, v, mask, w)
+    for m_dev in (mask.to(DEV).contiguous(), wide.to(DEV)[..., 4:S + 4]):
+        qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+        out = sa.sparse_attention(qd, kd, vd, m_dev, bq, bk, check_status=True)
+        out.backward(w.to(DEV))
+        torch.cuda.synchronize()
+        for name, got, ref in zip(("dq", "dk", "dv"), (qd.grad, kd.grad, vd.grad), want):
+            _assert_grad_close(got, ref, dtype, f"{name} {dtype} D={D} ({bq},{bk}) mask stride {m_dev.stride(2)}")
