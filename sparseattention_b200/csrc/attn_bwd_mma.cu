@@ -268,9 +268,11 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
   if (total_chunks > 0) request(0);
 #pragma unroll 1
   for (int u = 0; u < total_chunks; ++u) {
-    // the next chunk travels while this one is worked on
-    if (u + 1 < total_chunks) { request(u + 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    // One barrier per chunk: behind it chunk u has landed for every thread, and every warp is done with
+    // chunk u-1, whose buffer the next chunk is then requested into (it travels while this one is worked on).
+    cp_async_wait<0>();
     __syncthreads();
+    if (u + 1 < total_chunks) request(u + 1);
     if (MODE == 0 && u == 0) {
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
@@ -370,7 +372,6 @@ attn_bwd_mma_kernel(const AttnBwdParams p, const int mask_vec) {
         }
       }
     }
-    __syncthreads();                                // every warp is done with this buffer before it is requested again
   }
   cp_async_wait<0>();
 
