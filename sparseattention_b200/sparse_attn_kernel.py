@@ -159,8 +159,19 @@ def sparse_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
             Sq % int(BLOCK_Q) == 0 and Sk % int(BLOCK_K) == 0 and \
             _native.uses_tcgen05(k[:, :, :128], k, v, 128, int(BLOCK_K), True):   # the padded q is fresh and dense: k stands in
         q = _pad_rows(q, pad_rows)
-        mask = _pad_rows(_native._distinct_planes(mask), pad_rows).expand(B, H, Sq + pad_rows, Sk)
-        BLOCK_Q, cache = 128, False
+        BLOCK_Q = 128
+        hit = _MASK_CACHE.get(_cache_key(mask, 128, BLOCK_K) + ("padded",)) if cache else None
+        if hit is not None:                     # the lists and the padded copy made for this mask memory before
+            md, mask = hit[0], hit[2]
+        else:
+            padded = _pad_rows(_native._distinct_planes(mask), pad_rows).expand(B, H, Sq + pad_rows, Sk)
+            if cache:
+                md = compute_mask_kernel(padded, 128, BLOCK_K)
+                _MASK_CACHE[_cache_key(mask, 128, BLOCK_K) + ("padded",)] = (md, mask, padded)
+                while len(_MASK_CACHE) > MASK_CACHE_ENTRIES:
+                    _MASK_CACHE.popitem(last=False)
+            mask = padded
+        cache = False
     else:
         pad_rows = 0
     if md is None and int(BLOCK_Q) in (32, 64) and impl_id != _native.SA_IMPL_SIMT and \

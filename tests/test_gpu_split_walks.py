@@ -95,3 +95,28 @@ def test_c_abi_refuses_what_it_cannot_split(native_lib):
     kv = torch.randn((1, 1, 512, 64), device=DEV, dtype=torch.float32)
     with pytest.raises(NotImplementedError):
         sa.sparse_attention(q, kv, kv, mask, 128, 32, splits=2)
+
+
+def test_cache_keeps_the_padded_mask_and_its_lists(native_lib):
+    """``cache=True`` on a short query length: the second call finds the lists (and the padded copy of the
+    mask) made by the first; an in-place edit of the caller's mask misses."""
+    B, H, Sq, Sk, D = 1, 2, 32, 4096, 128
+    q, k, v = (torch.randn((B, H, s, D), generator=torch.Generator().manual_seed(i)).to(torch.bfloat16).to(DEV)
+               for i, s in ((1, Sq), (2, Sk), (3, Sk)))
+    mask = _decode_mask(B, Sq, Sk, 0.4, seed=3).to(DEV)
+    sa.clear_mask_cache()
+    first = sa.sparse_attention(q, k, v, mask, 32, 32, cache=True)
+    calls = []
+    real = sa.sparse_attn_kernel.compute_mask_kernel
+    sa.sparse_attn_kernel.compute_mask_kernel = lambda *a, **kw: (calls.append(1), real(*a, **kw))[1]
+    try:
+        second = sa.sparse_attention(q, k, v, mask, 32, 32, cache=True)
+        assert not calls and torch.equal(first, second)
+        mask[..., 100:200] = False
+        third = sa.sparse_attention(q, k, v, mask, 32, 32, cache=True)
+        assert calls
+    finally:
+        sa.sparse_attn_kernel.compute_mask_kernel = real
+        sa.clear_mask_cache()
+    ref = sdpa_cpu(q.cpu(), k.cpu(), v.cpu(), mask.cpu().expand(B, H, Sq, Sk))
+    assert_close_attn(third, ref, torch.bfloat16, "after the edit")
