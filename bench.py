@@ -420,6 +420,8 @@ def run_decode(args):
     io_bytes = kv_bytes + 2 * B * H * Sq * D * 2            # + Q read, O written
     res = {}
     res["call_ms"] = best_ms(lambda: sa.sparse_attention(q, k, v, mask, Sq, BK), n=7, warm=3)
+    res["call_cached_ms"] = best_ms(lambda: sa.sparse_attention(q, k, v, mask, Sq, BK, cache=True), n=7, warm=3)
+    sa.clear_mask_cache()
     res["attention_ms"] = best_ms(lambda: sa.sparse_attention(q128, k, v, mask128, 128, BK, mask_metadata=md), n=7, warm=3)
     res["attention_unsplit_ms"] = best_ms(
         lambda: sa.sparse_attention(q128, k, v, mask128, 128, BK, mask_metadata=md, splits=1), n=5, warm=2)
